@@ -28,7 +28,7 @@ NO_PAGE = -1
 
 class PageGroup:
     """Layers with identical needs: one allocator, one device tensor
-    ``[layers, 2 (K, V), pages, page_size, kv_heads, head_dim]``."""
+    ``[layers, planes (K, V; or one row per token), pages, page_size, kv_heads, head_dim]``."""
 
     def __init__(self, need: PagedKVNeed, cache_layers: list[int], num_pages: int, page_size: int,
                  dtype: torch.dtype | None, device) -> None:
@@ -39,18 +39,18 @@ class PageGroup:
         self.kv: torch.Tensor | None = None
         if device is not None and dtype is not None:
             self.kv = torch.zeros(
-                (len(cache_layers), 2, num_pages, page_size, need.num_kv_heads, need.head_dim),
+                (len(cache_layers), need.planes, num_pages, page_size, need.num_kv_heads, need.head_dim),
                 dtype=dtype, device=device,
             )
         self._index = {layer: i for i, layer in enumerate(self.cache_layers)}
 
     def layer_kv(self, cache_layer: int) -> tuple[torch.Tensor, torch.Tensor]:
         plane = self.kv[self._index[cache_layer]]
-        return plane[0], plane[1]
+        return plane[0], plane[self.need.planes - 1]
 
     def bytes_per_token(self) -> int:
         elem = self.kv.element_size() if self.kv is not None else 2
-        return len(self.cache_layers) * 2 * self.need.num_kv_heads * self.need.head_dim * elem
+        return len(self.cache_layers) * self.need.planes * self.need.num_kv_heads * self.need.head_dim * elem
 
 
 @dataclass
@@ -254,7 +254,7 @@ class CacheManager:
             return
         from .. import ops
 
-        planes = group.kv.view(group.kv.shape[0] * 2, *group.kv.shape[2:])
+        planes = group.kv.view(group.kv.shape[0] * group.kv.shape[1], *group.kv.shape[2:])
         pairs = torch.tensor([[src, dst]], dtype=torch.int32, device=group.kv.device)
         ops.copy_pages(planes, pairs, self.status)
 

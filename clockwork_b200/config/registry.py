@@ -73,6 +73,11 @@ def shape_config(name: str, num_layers: int | None = None) -> dict[str, Any]:
 
 
 def architecture_name(raw: dict[str, Any]) -> str:
+    """``config.json`` names its architecture as ``"architectures": [name]`` (the Hugging Face form) or as
+    ``"architecture": name``."""
+    single = raw.get("architecture")
+    if isinstance(single, str) and "architectures" not in raw:
+        return single
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ValueError(

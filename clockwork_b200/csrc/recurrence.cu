@@ -1,0 +1,349 @@
+// Layers that carry a state of fixed size from token to token instead of a cache of keys: the
+// pieces that a state-space layer (Mamba-2 form) and a linear-attention layer with per-channel decay
+// (RWKV form) are put together from.  Every kernel takes one flat batch of tokens (prompt portions
+// beside single decoded tokens): request s owns rows q_start[s] .. q_start[s+1]-1, its state lives in
+// row slots[s] of a float32 table [slots, state_stride], and a portion continues from whatever the
+// step before left there.  Rows whose tok_seq is negative are padding of a fixed-shape step.
+//
+//   cw_shift_mix        m_s = x + (x_prev - x) * mu_s for several mu at once; x_prev of a portion's
+//                       first row is the row that cw_carry_rows kept
+//   cw_causal_conv      per-channel causal convolution over the last `taps` inputs, bias, SiLU; the
+//                       inputs before a portion's first row are the rows that cw_carry_rows kept
+//   cw_carry_rows       keeps the last R rows of each request's portion for the next step
+//   cw_recurrence_scan  S <- diag(a_t) S + k_t v_t^T, y_t = S^T q_t, in the two forms named below,
+//                       float32 state, one pass over the portion in token order
+//   cw_gated_group_norm y (*silu(z)) divided by its root mean square in equal parts, times a weight
+//                       (times silu(z)): the gate before or after the norm
+//   cw_activation       gelu (tanh form), tanh, in place
+//
+// Everything that enters the recurrence (decays, step sizes, the state, the norm) is float32 in both
+// run precisions; T only names the type of activations that matrix products read or wrote.
+#include "common.cuh"
+
+// ---- token shift ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const float* __restrict__ state,
+                 long long state_stride, long long state_off, const long long* __restrict__ slots,
+                 const int* __restrict__ tok_seq, const int* __restrict__ q_start, T* __restrict__ out,
+                 int N, int W, int mixes) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int seq = tok_seq[row];
+    const size_t plane = (size_t)N * W;
+    if (seq < 0) {
+        for (int c = threadIdx.x; c < W; c += blockDim.x)
+            for (int s = 0; s < mixes; ++s) out[s * plane + (size_t)row * W + c] = from_f<T>(0.f);
+        return;
+    }
+    const bool first = row == q_start[seq];
+    const float* kept = state + slots[seq] * state_stride + state_off;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float cur = to_f(x[(size_t)row * W + c]);
+        const float prev = first ? kept[c] : to_f(x[(size_t)(row - 1) * W + c]);
+        const float d = prev - cur;
+        for (int s = 0; s < mixes; ++s)
+            out[s * plane + (size_t)row * W + c] = from_f<T>(fmaf(d, mu[(size_t)s * W + c], cur));
+    }
+}
+
+extern "C" int cw_shift_mix(const void* x, const float* mu, const float* state, long long state_stride,
+                            long long state_off, const long long* slots, const int* tok_seq, const int* q_start,
+                            void* out, int N, int W, int mixes, int dtype, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0 || mixes <= 0) return CW_ERR_BAD_SIZE;
+    if (dtype == 0)
+        return cw_launch(shift_mix_kernel<float>, dim3(N), dim3(256), 0, stream, 1, (const float*)x, mu, state, state_stride,
+                         state_off, slots, tok_seq, q_start, (float*)out, N, W, mixes);
+    if (dtype == 1)
+        return cw_launch(shift_mix_kernel<bf16>, dim3(N), dim3(256), 0, stream, 1, (const bf16*)x, mu, state, state_stride,
+                         state_off, slots, tok_seq, q_start, (bf16*)out, N, W, mixes);
+    return CW_ERR_BAD_DTYPE;
+}
+
+// ---- short causal convolution ---------------------------------------------------------------------
+// x [N, ldx] float32 (a column slice of a wider matrix), weight [C, taps] with the current token's tap
+// last, out [N, C] float32 = silu(bias + sum_j weight[c][j] * x[row - (taps-1-j)][c]).
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ weight, const float* __restrict__ bias,
+                   const float* __restrict__ state, long long state_stride, long long state_off,
+                   const long long* __restrict__ slots, const int* __restrict__ tok_seq, const int* __restrict__ q_start,
+                   float* __restrict__ out, int C, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int seq = tok_seq[row];
+    if (seq < 0) {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)row * C + c] = 0.f;
+        return;
+    }
+    const int start = q_start[seq];
+    const int R = taps - 1;
+    const float* kept = state + slots[seq] * state_stride + state_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = bias != nullptr ? bias[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = row - (R - j);
+            const float v = src >= start ? x[(size_t)src * ldx + c] : kept[(size_t)(R - (start - src)) * C + c];
+            acc = fmaf(weight[(size_t)c * taps + j], v, acc);
+        }
+        out[(size_t)row * C + c] = acc / (1.f + expf(-acc));
+    }
+}
+
+extern "C" int cw_causal_conv(const float* x, int ldx, const float* weight, const float* bias, const float* state,
+                              long long state_stride, long long state_off, const long long* slots, const int* tok_seq,
+                              const int* q_start, float* out, int N, int C, int taps, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || C <= 0 || taps <= 0 || ldx < C) return CW_ERR_BAD_SIZE;
+    return cw_launch(causal_conv_kernel, dim3(N), dim3(256), 0, stream, 1, x, ldx, weight, bias, state, state_stride, state_off,
+                     slots, tok_seq, q_start, out, C, taps);
+}
+
+// ---- the rows a later step reads again --------------------------------------------------------------
+// kept[R][C] of a request: kept[R-d] is the row d places before the request's next token.  A portion of
+// n rows shifts the older rows up by n and appends its own last min(n, R).
+template <typename T>
+__global__ void __launch_bounds__(256)
+carry_rows_kernel(const T* __restrict__ x, int ldx, float* __restrict__ state, long long state_stride,
+                  long long state_off, const long long* __restrict__ slots, const int* __restrict__ tok_seq,
+                  const int* __restrict__ q_start, int C, int R) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x;
+    const int start = q_start[seq], end = q_start[seq + 1];
+    const int n = end - start;
+    if (n <= 0 || tok_seq[start] < 0) return;
+    float* kept = state + slots[seq] * state_stride + state_off;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        for (int d = R; d >= 1; --d)  // ascending writes; what is read lies ahead of what was written
+            kept[(size_t)(R - d) * C + c] = d <= n ? to_f(x[(size_t)(end - d) * ldx + c]) : kept[(size_t)(R - (d - n)) * C + c];
+    }
+}
+
+extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long state_stride, long long state_off,
+                             const long long* slots, const int* tok_seq, const int* q_start, int S, int C, int R, int dtype,
+                             cudaStream_t stream) {
+    if (S == 0 || R == 0) return CW_OK;
+    if (S < 0 || C <= 0 || R < 0 || ldx < C) return CW_ERR_BAD_SIZE;
+    dim3 grid(S, min(64, (C + 255) / 256));
+    if (dtype == 0)
+        return cw_launch(carry_rows_kernel<float>, grid, dim3(256), 0, stream, 1, (const float*)x, ldx, state, state_stride,
+                         state_off, slots, tok_seq, q_start, C, R);
+    if (dtype == 1)
+        return cw_launch(carry_rows_kernel<bf16>, grid, dim3(256), 0, stream, 1, (const bf16*)x, ldx, state, state_stride,
+                         state_off, slots, tok_seq, q_start, C, R);
+    return CW_ERR_BAD_DTYPE;
+}
+
+// ---- the recurrence ---------------------------------------------------------------------------------
+// Per request and head a state S [Dk, Dv] (float32, stored value-column-major: element (i, j) of head h at
+// (h*Dv + j)*Dk + i).  Two forms:
+//   FORM 0 (decay per key channel, output before the update, bonus for the current token):
+//       a_i = exp(-exp(pre_i + p0_i));  y_j = sum_i q_i (S_ij + p1_i k_i v_j);  S_ij <- a_i S_ij + k_i v_j
+//   FORM 1 (one decay per head from a step size, output after the update, skip term):
+//       dt = softplus(pre + p0);  a = exp(-exp(p1) dt);  S_ij <- a S_ij + dt k_i v_j;  y_j = sum_i q_i S_ij + p2 v_j
+// q and k of head h are those of group h / heads_per_group.  A thread owns up to RS consecutive key
+// channels of one value column; the IP threads of a column are neighbouring lanes of a warp and sum up by
+// shuffles, so a token costs no block-wide barrier.  Blocks: (request, head, slice of value columns).
+#define RS 8
+template <int FORM>
+__global__ void __launch_bounds__(128)
+recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                       const float* __restrict__ v, int ldv, const float* __restrict__ pre, int ldp,
+                       const float* __restrict__ p0, const float* __restrict__ p1, const float* __restrict__ p2,
+                       float* __restrict__ state, long long state_stride, long long state_off,
+                       const long long* __restrict__ slots, const int* __restrict__ tok_seq,
+                       const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP,
+                       float* __restrict__ out, int ldo) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int start = q_start[seq], end = q_start[seq + 1];
+    if (end <= start) return;
+    const int ipart = threadIdx.x % IP, jl = threadIdx.x / IP, JB = blockDim.x / IP;
+    const int j = blockIdx.z * JB + jl;
+    const bool live = j < Dv;
+    if (tok_seq[start] < 0) {  // padding rows of a fixed-shape step: no request, no state
+        if (live && ipart == 0)
+            for (int t = start; t < end; ++t) out[(size_t)t * ldo + (size_t)h * Dv + j] = 0.f;
+        return;
+    }
+    const int R = (Dk + IP - 1) / IP;
+    const int i0 = ipart * R;
+    const int g = h / heads_per_group;
+    float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
+    float S[RS], c0[RS], c1[RS];
+#pragma unroll
+    for (int r = 0; r < RS; ++r) {
+        const int i = i0 + r;
+        const bool on = r < R && i < Dk;
+        S[r] = (on && live) ? S_mem[i] : 0.f;
+        if (FORM == 0) {
+            c0[r] = on ? p0[(size_t)h * Dk + i] : 0.f;
+            c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
+        }
+    }
+    float head_p0 = 0.f, head_decay = 0.f, head_skip = 0.f;
+    if (FORM == 1) {
+        head_p0 = p0[h];
+        head_decay = expf(p1[h]);
+        head_skip = p2 != nullptr ? p2[h] : 0.f;
+    }
+    const float* qp = q + (size_t)g * Dk;
+    const float* kp = k + (size_t)g * Dk;
+    const float* pp = FORM == 0 ? pre + (size_t)h * Dk : pre + h;
+    const float* vp = v + (size_t)h * Dv + (live ? j : 0);
+    float qn[RS], kn[RS], an[RS], vn, dn = 0.f;
+    // the next token's operands are fetched while the current one is computed
+    auto fetch = [&](int t) {
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            const int i = i0 + r;
+            const bool on = r < R && i < Dk;
+            qn[r] = on ? qp[(size_t)t * ldq + i] : 0.f;
+            kn[r] = on ? kp[(size_t)t * ldk + i] : 0.f;
+            if (FORM == 0) an[r] = on ? pp[(size_t)t * ldp + i] : 0.f;
+        }
+        if (FORM == 1) dn = pp[(size_t)t * ldp];
+        vn = vp[(size_t)t * ldv];
+    };
+    fetch(start);
+    for (int t = start; t < end; ++t) {
+        float qc[RS], kc[RS], ac[RS];
+        const float vc = vn, dc = dn;
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            qc[r] = qn[r];
+            kc[r] = kn[r];
+            if (FORM == 0) ac[r] = an[r];
+        }
+        if (t + 1 < end) fetch(t + 1);
+        float part = 0.f;
+        if (FORM == 0) {
+#pragma unroll
+            for (int r = 0; r < RS; ++r) {
+                const float a = expf(-expf(ac[r] + c0[r]));
+                const float kv = kc[r] * vc;
+                part = fmaf(qc[r], fmaf(c1[r], kv, S[r]), part);
+                S[r] = fmaf(a, S[r], kv);
+            }
+        } else {
+            const float x = dc + head_p0;
+            const float dt = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // softplus without a threshold
+            const float a = expf(-head_decay * dt);
+#pragma unroll
+            for (int r = 0; r < RS; ++r) {
+                S[r] = fmaf(a, S[r], dt * kc[r] * vc);
+                part = fmaf(qc[r], S[r], part);
+            }
+        }
+        for (int o = 1; o < IP; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (live && ipart == 0) out[(size_t)t * ldo + (size_t)h * Dv + j] = FORM == 1 ? fmaf(head_skip, vc, part) : part;
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            const int i = i0 + r;
+            if (r < R && i < Dk) S_mem[i] = S[r];
+        }
+    }
+}
+
+extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                  const float* pre, int ldp, const float* p0, const float* p1, const float* p2,
+                                  float* state, long long state_stride, long long state_off, const long long* slots,
+                                  const int* tok_seq, const int* q_start, int S, int H, int Dk, int Dv, int heads_per_group, float* out, int ldo,
+                                  cudaStream_t stream) {
+    if (S == 0) return CW_OK;
+    if (S < 0 || H <= 0 || Dk <= 0 || Dv <= 0 || heads_per_group <= 0 || H % heads_per_group) return CW_ERR_BAD_SIZE;
+    if (Dk > 32 * RS || H > 65535) return CW_ERR_UNSUPPORTED;
+    int IP = 1;
+    while (IP * RS < Dk) IP *= 2;
+    const int JB = 128 / IP;
+    dim3 grid(S, H, (Dv + JB - 1) / JB);
+    if (form == 0)
+        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(128), 0, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
+    if (form == 1)
+        return cw_launch(recurrence_scan_kernel<1>, grid, dim3(128), 0, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
+    return CW_ERR_UNSUPPORTED;
+}
+
+// ---- gated norm in parts ----------------------------------------------------------------------------
+// y [N, C] float32, gate z [N, ldz] float32.  gate_first: u = y silu(z), out = u / rms_part(u) * weight.
+// Otherwise: out = y / rms_part(y) * weight * silu(z).  A warp per part.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ weight,
+                        T* __restrict__ out, int C, int parts, float eps, int gate_first) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int width = C / parts;
+    for (int p = warp; p < parts; p += warps) {
+        const float* yr = y + (size_t)row * C + (size_t)p * width;
+        const float* zr = z + (size_t)row * ldz + (size_t)p * width;
+        float ss = 0.f;
+        for (int c = lane; c < width; c += 32) {
+            float u = yr[c];
+            if (gate_first) {
+                const float g = zr[c];
+                u *= g / (1.f + expf(-g));
+            }
+            ss = fmaf(u, u, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+        for (int c = lane; c < width; c += 32) {
+            const float g = zr[c];
+            const float sg = g / (1.f + expf(-g));
+            const float u = gate_first ? yr[c] * sg : yr[c];
+            float r = u * inv * weight[(size_t)p * width + c];
+            if (!gate_first) r *= sg;
+            out[(size_t)row * C + (size_t)p * width + c] = from_f<T>(r);
+        }
+    }
+}
+
+extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, const float* weight, void* out, int N, int C,
+                                   int parts, float eps, int gate_first, int dtype, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || C <= 0 || parts <= 0 || C % parts || ldz < C) return CW_ERR_BAD_SIZE;
+    if (dtype == 0)
+        return cw_launch(gated_group_norm_kernel<float>, dim3(N), dim3(128), 0, stream, 1, y, z, ldz, weight, (float*)out, C, parts,
+                         eps, gate_first);
+    if (dtype == 1)
+        return cw_launch(gated_group_norm_kernel<bf16>, dim3(N), dim3(128), 0, stream, 1, y, z, ldz, weight, (bf16*)out, C, parts,
+                         eps, gate_first);
+    return CW_ERR_BAD_DTYPE;
+}
+
+// ---- activations in place -----------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(T* __restrict__ x, long long n, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float z = to_f(x[i]);
+        float r;
+        if (kind == 0)
+            r = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        else
+            r = tanhf(z);
+        x[i] = from_f<T>(r);
+    }
+}
+
+extern "C" int cw_activation(void* x, long long n, int kind, int dtype, cudaStream_t stream) {
+    if (n == 0) return CW_OK;
+    if (n < 0 || kind < 0 || kind > 1) return CW_ERR_BAD_SIZE;
+    const int blocks = (int)min((long long)148 * 8, (n + 255) / 256);
+    if (dtype == 0) return cw_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (float*)x, n, kind);
+    if (dtype == 1) return cw_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (bf16*)x, n, kind);
+    return CW_ERR_BAD_DTYPE;
+}
+
+CW_TRACE_TU(recurrence)

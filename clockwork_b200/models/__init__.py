@@ -1,6 +1,7 @@
 """Architectures.  Importing this package registers each of them by name."""
 
-from . import qwen2  # noqa: F401
+from . import qwen2, rapitar  # noqa: F401
 from .qwen2 import Qwen2Architecture, Qwen2Config
+from .rapitar import RapitarArchitecture, RapitarConfig
 
-__all__ = ["Qwen2Architecture", "Qwen2Config"]
+__all__ = ["Qwen2Architecture", "Qwen2Config", "RapitarArchitecture", "RapitarConfig"]

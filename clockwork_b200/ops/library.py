@@ -30,6 +30,21 @@ _SIGNATURES: dict[str, list] = {
     "cw_sample_rows": [P, P, P, P, P, P, I, I, LL, P, P, I, P, P],
     "cw_sample_workspace_words": [I],
     "cw_step_from_state": [P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P],
+    # layers with a state of fixed size (csrc/recurrence.cu)
+    "cw_shift_mix": [P, P, P, LL, LL, P, P, P, P, I, I, I, I, P],
+    "cw_causal_conv": [P, I, P, P, P, LL, LL, P, P, P, P, I, I, I, P],
+    "cw_carry_rows": [P, I, P, LL, LL, P, P, P, I, I, I, I, P],
+    "cw_recurrence_scan": [I, P, I, P, I, P, I, P, I, P, P, P, P, LL, LL, P, P, P, I, I, I, I, I, P, I, P],
+    "cw_gated_group_norm": [P, P, I, P, P, I, I, I, F, I, I, P],
+    "cw_activation": [P, LL, I, I, P],
+    # products in groups and the mixture of experts (csrc/grouped_gemm.cu)
+    "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, I, P],
+    "cw_moe_route": [P, P, P, P, P, P, I, I, I, I, I, P],
+    "cw_moe_group": [P, P, P, P, I, I, P],
+    "cw_moe_combine": [P, P, P, P, I, I, I, P],
+    # attention over a cached latent (csrc/latent_attention.cu)
+    "cw_latent_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P, P],
+    "cw_latent_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
 }
 _OPTIONAL: dict[str, list] = {}
 

@@ -1,7 +1,7 @@
 """Parts: norms, position encodings, mixers, feed-forwards, blocks, and the model made of them.
 Importing this package registers the built-in kinds."""
 
-from . import attention, block, rmsnorm, rotary, swiglu  # noqa: F401  (registration)
+from . import attention, block, feedforward, latent_attention, parallel_block, rmsnorm, rotary, state_mixers, swiglu  # noqa: F401  (registration)
 from .base import (
     Block, FeedForward, Mixer, Norm, PagedKVNeed, PagedView, Part, PositionEncoding,
     ResidualStream, SlotStateNeed, StateView, StepContext,

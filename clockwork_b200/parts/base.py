@@ -35,11 +35,14 @@ Fetch = Callable[[str], torch.Tensor]
 @dataclass(frozen=True)
 class PagedKVNeed:
     """The mixer keeps keys and values per token, in pages.  ``window``: only the last
-    ``window`` tokens are ever read (pages behind it can be given back); None: all."""
+    ``window`` tokens are ever read (pages behind it can be given back); None: all.  ``planes``: 2 for
+    keys and values; 1 for a mixer that keeps one row per token (a latent that keys and values are both
+    made from): its view's ``k_cache`` and ``v_cache`` are then the same tensor."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -2,7 +2,10 @@
 
 Reference: ``clockwork/engine/model.py:38-49`` (float32 statistics, ``x * rsqrt(mean(x^2) +
 eps)``, then the weight) and ``:150``/``:154`` (the residual sums the norm kernel absorbs).
-Parameters: ``size``, ``eps``.  Tensor: ``<prefix>.weight`` [size], kept in float32.
+Parameters: ``size``, ``eps``; optional ``offset`` (added to the stored weight: with 1.0 the checkpoint holds the weight's
+distance from one and the norm multiplies by ``1 + w``) and ``weight_suffix`` (the tensor's name
+behind the prefix, ``weight`` by default; empty: the prefix itself is the name).  Tensor: [size], kept
+in float32.
 """
 
 from __future__ import annotations
@@ -25,13 +28,18 @@ class RMSNorm(Norm):
         super().__init__(spec, prefix, dtype, device)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.offset = float(spec.get("offset", 0.0))
+        suffix = spec.get("weight_suffix", "weight")
+        self.weight_name = self.name(suffix) if suffix else self.prefix
         self.weight: torch.Tensor | None = None
 
     def tensor_decls(self):
-        yield TensorDecl(self.name("weight"), (self.size,), role="vector", init="norm")
+        yield TensorDecl(self.weight_name, (self.size,), role="vector", init="zeros" if self.offset else "norm")
 
     def load_weights(self, fetch) -> None:
-        self.weight = fetch(self.name("weight"))
+        self.weight = fetch(self.weight_name)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()  # float32: exact for a weight stored in bfloat16
 
     def split_weight(self) -> torch.Tensor | None:
         """The weight a preceding product multiplies into the residual when it begins this norm."""

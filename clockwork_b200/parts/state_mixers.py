@@ -1,0 +1,149 @@
+"""Mixers that carry a state of fixed size per request instead of a cache of keys.
+
+``mamba2`` (state-space duality form).  Parameters: ``hidden_size, heads, vdim, state, groups, conv,
+norm_groups, eps``.  With inner = heads*vdim, the input product yields ``[z | x | B | C | dt]`` (widths
+inner, inner, groups*state, groups*state, heads).  x, B and C pass a causal per-channel convolution of
+``conv`` taps (tensor ``conv`` [channels, taps], the current token's tap last, bias ``conv.b``) and
+SiLU.  ``dt = softplus(dt + dt_bias)``; per head (its B and C are those of group head // (heads/groups)):
+``S <- exp(-exp(A_log) dt) S + dt B x^T`` (S is state x vdim), ``y = S^T C + D x``.  Then ``y silu(z)``
+is RMS-normed in ``norm_groups`` equal parts, times ``norm``, and goes through ``o``.  Per request the
+state slot holds S of every head and the last conv-1 inputs of the convolution.
+
+``wkv`` (time mixing in the manner of RWKV).  Parameters: ``hidden_size, heads, dim, eps``; the inner size of the decay's
+two products is whatever the checkpoint's ``w1`` has (``decay_rank`` only sizes random weights).  With x' the
+previous token's input (zeros before the first), each of r, k, v, g, w reads ``x + (x' - x) mu_s``;
+``r, k, v`` are products of their mixes, ``gate = silu(g product)``, ``w = exp(-exp(w2 tanh(w1 mix_w) + w0))``
+per head and key channel.  Per head ``o = (S + diag(u) k v^T)^T r`` and then ``S <- diag(w) S + k v^T``.
+Each head's o is divided by its root mean square, times ``norm``, times the gate, and goes through ``o``.
+The state slot holds S of every head and the previous token's input.
+
+Both run the recurrence itself, the decays, step sizes and norms in float32 in either run precision;
+the products that feed them write float32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import gemm as gemm_ops
+from ..ops import recurrence as rec_ops
+from ..weights.decl import TensorDecl
+from .base import Mixer, ResidualStream, SlotStateNeed, StateView, StepContext
+from .linear import Linear
+from .registry import register_mixer
+
+
+class Mamba2Mixer(Mixer):
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.vdim, self.state_size = int(p["heads"]), int(p["vdim"]), int(p["state"])
+        self.groups, self.taps, self.norm_groups = int(p["groups"]), int(p["conv"]), int(p["norm_groups"])
+        self.eps = float(p["eps"])
+        self.inner = self.heads * self.vdim
+        if self.heads % self.groups:
+            raise ValueError(f"heads {self.heads} not a multiple of groups {self.groups}")
+        if self.inner % self.norm_groups:
+            raise ValueError(f"inner size {self.inner} not a multiple of norm_groups {self.norm_groups}")
+        if self.taps < 1:
+            raise ValueError("conv must be at least 1")
+        self.channels = self.inner + 2 * self.groups * self.state_size
+        self.proj_width = 2 * self.inner + 2 * self.groups * self.state_size + self.heads
+        # the layout of a request's state row
+        self.scan_offset = 0
+        self.conv_offset = self.heads * self.state_size * self.vdim
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.conv_offset + (self.taps - 1) * self.channels,))
+
+    def tensor_decls(self):
+        yield TensorDecl(self.name("in"), (self.proj_width, self.hidden_size), "matrix", "linear")
+        yield TensorDecl(self.name("conv"), (self.channels, self.taps), "vector", "norm")
+        yield TensorDecl(self.name("conv.b"), (self.channels,), "vector", "bias")
+        yield TensorDecl(self.name("dt_bias"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("A_log"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("D"), (self.heads,), "vector", "norm")
+        yield TensorDecl(self.name("norm"), (self.inner,), "vector", "norm")
+        yield TensorDecl(self.name("o"), (self.hidden_size, self.inner), "matrix", "linear")
+
+    def load_weights(self, fetch) -> None:
+        self.w_in = Linear(fetch(self.name("in")))
+        self.conv_w, self.conv_b = fetch(self.name("conv")), fetch(self.name("conv.b"))
+        self.dt_bias, self.a_log, self.skip = fetch(self.name("dt_bias")), fetch(self.name("A_log")), fetch(self.name("D"))
+        self.norm_w = fetch(self.name("norm"))
+        self.o = Linear(fetch(self.name("o")))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        inner, gn = self.inner, self.groups * self.state_size
+        proj = self.w_in.to_float32(x)  # [N, z | x | B | C | dt], float32
+        xbc_raw = proj[:, inner : inner + self.channels]
+        xbc = rec_ops.causal_conv(xbc_raw, self.conv_w, self.conv_b, view, self.conv_offset, ctx)
+        rec_ops.carry_rows(xbc_raw, self.taps - 1, view, self.conv_offset, ctx)  # after the convolution has read the old rows
+        y = rec_ops.recurrence_scan(
+            rec_ops.FORM_STEP_SIZE, q=xbc[:, inner + gn :], k=xbc[:, inner : inner + gn], v=xbc[:, :inner],
+            pre=proj[:, inner + self.channels :], p0=self.dt_bias, p1=self.a_log, p2=self.skip, view=view,
+            offset=self.scan_offset, ctx=ctx, heads=self.heads, dk=self.state_size, dv=self.vdim,
+            heads_per_group=self.heads // self.groups)
+        out = rec_ops.gated_group_norm(y, proj[:, :inner], self.norm_w, self.norm_groups, self.eps, True, self.dtype)
+        return self.o.add_or_defer(out, stream)
+
+
+class WkvMixer(Mixer):
+    graph_safe = True
+    graph_safe_portions = True
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.dim, self.decay_rank = int(p["heads"]), int(p["dim"]), int(p.get("decay_rank") or 32)
+        self.eps = float(p["eps"])
+        self.inner = self.heads * self.dim
+        self.scan_offset = 0
+        self.shift_offset = self.heads * self.dim * self.dim
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.shift_offset + self.hidden_size,))
+
+    def tensor_decls(self):
+        h, a = self.hidden_size, self.inner
+        for s in self.MIXES:
+            yield TensorDecl(self.name(f"mu.{s}"), (h,), "vector", "bias")
+        for s in ("r", "k", "v", "g"):
+            yield TensorDecl(self.name(s), (a, h), "matrix", "linear")
+        yield TensorDecl(self.name("w1"), (self.decay_rank, h), "matrix", "linear", free_dims=(0,))
+        yield TensorDecl(self.name("w2"), (a, self.decay_rank), "matrix", "linear", free_dims=(1,))
+        yield TensorDecl(self.name("w0"), (a,), "vector", "bias")
+        yield TensorDecl(self.name("u"), (self.heads, self.dim), "vector", "bias")
+        yield TensorDecl(self.name("norm"), (a,), "vector", "norm")
+        yield TensorDecl(self.name("o"), (h, a), "matrix", "linear")
+
+    def load_weights(self, fetch) -> None:
+        self.mu = torch.stack([fetch(self.name(f"mu.{s}")) for s in self.MIXES]).contiguous()
+        self.w_r, self.w_k, self.w_v, self.w_g = (Linear(fetch(self.name(s))) for s in ("r", "k", "v", "g"))
+        self.w1, self.w2 = Linear(fetch(self.name("w1"))), Linear(fetch(self.name("w2")))
+        if self.w1.out_features != self.w2.in_features:
+            raise ValueError(f"{self.name('w1')} has {self.w1.out_features} rows, {self.name('w2')} {self.w2.in_features} columns")
+        self.w0 = fetch(self.name("w0"))
+        self.bonus = fetch(self.name("u")).reshape(-1).contiguous()
+        self.norm_w = fetch(self.name("norm"))
+        self.o = Linear(fetch(self.name("o")))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        mixes = rec_ops.shift_mix(x, self.mu, view, self.shift_offset, ctx)  # [5, N, H]
+        rec_ops.carry_rows(x, 1, view, self.shift_offset, ctx)  # after the mixes have read the old row
+        r, k, v, g = (w.to_float32(mixes[i]) for i, w in enumerate((self.w_r, self.w_k, self.w_v, self.w_g)))
+        pre = self.w2.to_float32(rec_ops.activation_(self.w1(mixes[4]), rec_ops.ACT_TANH))
+        o = rec_ops.recurrence_scan(rec_ops.FORM_CHANNEL_DECAY, q=r, k=k, v=v, pre=pre, p0=self.w0, p1=self.bonus, p2=None,
+                                    view=view, offset=self.scan_offset, ctx=ctx, heads=self.heads, dk=self.dim, dv=self.dim)
+        out = rec_ops.gated_group_norm(o, g, self.norm_w, self.heads, self.eps, False, self.dtype)
+        return self.o.add_or_defer(out, stream)
+
+
+register_mixer("mamba2", Mamba2Mixer, replace=True)
+register_mixer("wkv", WkvMixer, replace=True)

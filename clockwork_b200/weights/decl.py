@@ -27,6 +27,8 @@ class TensorDecl:
     role: str = "matrix"
     init: str = "linear"
     optional: bool = False  # may be absent from (or present in) the checkpoint without error
+    free_dims: tuple[int, ...] = ()  # dimensions whose size the checkpoint decides (the configuration does not name it);
+    # ``shape`` holds the size that the random-weights mode uses there
 
     def __post_init__(self) -> None:
         if self.role not in ROLES:

@@ -47,10 +47,15 @@ def check_declarations(decls: Iterable[TensorDecl], shapes: dict[str, tuple[int,
         raise ValueError(f"model declares tensors twice: {sorted(set(dup))}")
     missing = sorted(n for n, d in by_name.items() if n not in shapes and not d.optional)
     unexpected = sorted(n for n in shapes if n not in by_name)
+    def differs(got, decl) -> bool:
+        if len(got) != len(decl.shape):
+            return True
+        return any(g != w for i, (g, w) in enumerate(zip(got, decl.shape)) if i not in decl.free_dims)
+
     wrong = sorted(
         (n, tuple(shapes[n]), tuple(d.shape))
         for n, d in by_name.items()
-        if n in shapes and not d.optional and tuple(shapes[n]) != tuple(d.shape)
+        if n in shapes and not d.optional and differs(tuple(shapes[n]), d)
     )
     if missing or unexpected or wrong:
         raise WeightMismatchError(missing, unexpected, wrong, where)
