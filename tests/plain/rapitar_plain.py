@@ -72,7 +72,7 @@ def routed_ff(h, w, p, cfg, rnd=exact):
 
 
 def causal_conv_silu(x, weight, bias):
-    """x [T, C]; weight [C, taps], the last column is the current token's; zeros before the start."""
+    """x [T, C]; weight [C, taps]: the newest input meets the last tap, inputs before position 0 count as zero."""
     t, c = x.shape
     taps = weight.shape[1]
     padded = torch.cat([torch.zeros(taps - 1, c, dtype=x.dtype), x])
@@ -182,6 +182,13 @@ def feed_forward(h, w, p, cfg, rnd=exact):
     if cfg["kind"] == "moe":
         return routed_ff(h, w, p, cfg, rnd)
     raise ValueError(cfg["kind"])
+
+
+def greedy_generate(config, w, prompt, count, dtype=torch.float64):
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(forward(config, w, tokens, dtype=dtype)[-1].argmax()))
+    return tokens[len(prompt):]
 
 
 def forward(config, w, tokens, rnd=exact, dtype=torch.float32, keep_layers=False):
