@@ -362,6 +362,80 @@ def reference_arm(args) -> int:
 # ---------------------------------------------------------------------------------------------------
 # this engine's arm
 # ---------------------------------------------------------------------------------------------------
+def compare_designs(args) -> int:
+    """``--only designs``: prefill and decode of the Rapitar design at layer sizes of published models of
+    2,048 width (``rapitar-2k``: time mixing, latent attention, state-space layers; dense and mixture-of-experts
+    feed-forwards; random weights) beside a Qwen2 decoder of the same width and layer count, through the same step
+    function: a prompt of 512 and of 2,048 tokens, and single-token steps at batch 1 and 8 behind 1,024 tokens.
+    With ``--layers N`` both models have N layers.  One JSON line; device time by CUDA events, medians."""
+    import torch
+
+    from clockwork_b200.cache import CacheManager
+    from clockwork_b200.cli import shape_config
+    from clockwork_b200.engine import ModelRunner, StepEntry, random_model
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(0)
+    rapitar = shape_config("rapitar-2k", args.layers)
+    layers = len(rapitar["layers"])
+    qwen = dict(QWEN25_1P5B, num_hidden_layers=layers, hidden_size=2048, num_attention_heads=16, num_key_value_heads=2,
+                intermediate_size=7168, vocab_size=rapitar["vocab"], tie_word_embeddings=False)
+    rng = random.Random(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")  # larger than L2: written between timed calls
+    out = {"impl": "ours", "layers": layers, "width": 2048, "dtype": "bf16", "data": "synthetic", "l2": "flushed between timed calls"}
+    for name, raw, vocab in (("rapitar-2k", rapitar, rapitar["vocab"]), ("qwen2-2k", qwen, qwen["vocab_size"])):
+        model = random_model(raw, seed=0, dtype="bfloat16", device="cuda:0")
+        page, ctx, batch_max = 16, 1024, 8
+        cache = CacheManager(model.cache_needs(), num_pages=batch_max * (ctx + 256) // page + 160, page_size=page, dtype=model.dtype,
+                             device="cuda:0", num_state_slots=batch_max + 1)
+        runner = ModelRunner(model, cache)
+        runner.enable_graphs(max_ctx=4096, max_batch=batch_max)
+        result = {"weight_bytes": model.weight_bytes()}
+        for tokens in (512, 2048):
+            times = []
+            for rep in range(5):
+                cache.open("p")
+                toks = [rng.randrange(vocab) for _ in range(tokens)]
+                flush.fill_(rep)
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                runner.step([StepEntry("p", toks, [tokens - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                if rep >= 2:
+                    times.append(start.elapsed_time(end))
+                cache.close("p")
+            ms = statistics.median(times)
+            result[f"prefill_{tokens}"] = {"ms": ms, "tok_s": tokens / (ms / 1e3)}
+        for batch in (1, 8):
+            ids = [f"d{i}" for i in range(batch)]
+            for rid in ids:
+                cache.open(rid)
+                runner.step([StepEntry(rid, [rng.randrange(vocab) for _ in range(ctx)], [])])
+            times = []
+            for step in range(args.warmup + min(args.steps, 32)):
+                entries = [StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids]
+                flush.fill_(step)
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                runner.decode_with_graph(entries, None)
+                end.record()
+                torch.cuda.synchronize()
+                if step >= args.warmup:
+                    times.append(start.elapsed_time(end))
+            for rid in ids:
+                cache.close(rid)
+            ms = statistics.median(times)
+            result[f"decode_batch{batch}"] = {"ms_per_step": ms, "tok_s": batch / (ms / 1e3), "context": ctx}
+        runner.check_status()
+        out[name] = result
+        del runner, cache, model
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,7 +452,7 @@ def main() -> int:
     ap.add_argument("--shape", default="qwen2.5-1.5b",
                     help="with --only: another size that the architecture knows by name (qwen2.5-7b, qwen2.5-32b)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the points and the prefill (quick runs)")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix", "long-prompt"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix", "long-prompt", "designs"], default=None,
                     help="run one part only, once, and print its figures (for profiling runs under ncu)")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only decode: prompts of this many tokens instead of 1,024 (decoding at other context "
@@ -392,6 +466,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.only == "designs":
+        return compare_designs(args)
     if args.warmup < 3:
         args.warmup = 3
 

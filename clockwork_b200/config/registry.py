@@ -68,7 +68,11 @@ def shape_config(name: str, num_layers: int | None = None) -> dict[str, Any]:
     raw = dict(shapes[name])
     if num_layers is not None:
         arch = get_architecture(architecture_name(raw))
-        raw[getattr(arch, "layer_count_key", "num_hidden_layers")] = num_layers
+        key = getattr(arch, "layer_count_key", "num_hidden_layers")
+        if key is None:  # the layers are listed one by one: fewer layers are the first ones
+            raw["layers"] = list(raw["layers"][:num_layers])
+        else:
+            raw[key] = num_layers
     return raw
 
 

@@ -124,6 +124,192 @@ grouped_gemm_kernel(const T* __restrict__ A, int lda, int a_group_off, const T* 
     }
 }
 
+// ---- the same product on the tensor cores (bfloat16 operands, float32 accumulation) -------------------
+// Tiles of 64 rows x 128 outputs, K in steps of 32 through a three-stage cp.async ring, eight warps of
+// 32 x 32 outputs each on mma.sync m16n8k16.  A's rows are gathered through the index as they are
+// fetched.  Needs K, the row strides and the per-group offsets to be multiples of 8 elements (16-byte
+// copies); otherwise the kernel above runs.  A tile of few rows (single tokens) costs what its weights
+// cost to stream.
+#define GM_TM 64
+#define GM_TN 128
+#define GM_TK 32
+#define GM_LD 40  // padded row of a stage, in elements: 80 bytes, so that eight rows fall into distinct banks
+#define GM_STAGES 3
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(256)
+grouped_gemm_mma_kernel(const bf16* __restrict__ A, int lda, int a_group_off, const bf16* __restrict__ B,
+                        const bf16* __restrict__ B2, long long b_stride, void* __restrict__ Cv, int ldc, int c_group_off,
+                        const int* __restrict__ offsets, const int* __restrict__ a_index, int a_div,
+                        const int* __restrict__ c_index, const bf16* __restrict__ gate, int ldg,
+                        int M, int Nout, int K, int G) {
+    extern __shared__ __align__(16) unsigned char gm_smem[];
+    constexpr bool TWO = EPI == GG_EPI_SILU_MUL;
+    bf16* As = (bf16*)gm_smem;                       // [stages][TM][LD]
+    bf16* Bs = As + GM_STAGES * GM_TM * GM_LD;       // [stages][TN][LD]
+    bf16* B2s = Bs + GM_STAGES * GM_TN * GM_LD;      // [stages][TN][LD] (two-product form only)
+    __shared__ int src_s[GM_TM], dst_s[GM_TM];
+    pdl_launch_dependents();
+    pdl_wait();
+    int g, row0, rows_end;
+    if (offsets == nullptr) {
+        const int tiles = (M + GM_TM - 1) / GM_TM;
+        g = blockIdx.x / tiles;
+        row0 = (blockIdx.x % tiles) * GM_TM;
+        rows_end = M;
+    } else {
+        int tile = blockIdx.x;
+        g = 0;
+        while (g < G) {
+            const int n = offsets[g + 1] - offsets[g];
+            const int t = (n + GM_TM - 1) / GM_TM;
+            if (tile < t) break;
+            tile -= t;
+            ++g;
+        }
+        if (g >= G) return;
+        row0 = offsets[g] + tile * GM_TM;
+        rows_end = offsets[g + 1];
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < GM_TM) {
+        const int r = row0 + tid;
+        int s = -1, d = -1;
+        if (r < rows_end) {
+            s = a_index != nullptr ? a_index[r] / a_div : r;
+            d = c_index != nullptr ? c_index[r] : r;
+        }
+        src_s[tid] = s;
+        dst_s[tid] = d;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * GM_TN;
+    const bf16* Bg = B + (size_t)g * b_stride;
+    const bf16* B2g = TWO ? B2 + (size_t)g * b_stride : nullptr;
+    const int KT = (K + GM_TK - 1) / GM_TK;
+    auto load = [&](int kt, int stage) {
+        {
+            const int row = tid >> 2, k = kt * GM_TK + (tid & 3) * 8;
+            const int s = src_s[row];
+            const bool on = s >= 0 && k < K;
+            cp_async16(As + ((size_t)stage * GM_TM + row) * GM_LD + (tid & 3) * 8,
+                       on ? A + (size_t)s * lda + (size_t)g * a_group_off + k : A, on);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + i * 256;
+            const int n = idx >> 2, k = kt * GM_TK + (idx & 3) * 8;
+            const bool on = n0 + n < Nout && k < K;
+            const size_t at = ((size_t)stage * GM_TN + n) * GM_LD + (idx & 3) * 8;
+            cp_async16(Bs + at, on ? Bg + (size_t)(n0 + n) * K + k : Bg, on);
+            if (TWO) cp_async16(B2s + at, on ? B2g + (size_t)(n0 + n) * K + k : B2g, on);
+        }
+    };
+    const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps, 32 x 32 outputs each
+    float acc[2][4][4] = {}, acc2[TWO ? 2 : 1][TWO ? 4 : 1][4] = {};
+#pragma unroll
+    for (int s = 0; s < GM_STAGES - 1; ++s) {
+        if (s < KT) load(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(GM_STAGES - 2) : "memory");
+        __syncthreads();  // stage kt has landed for everyone, and everyone is done with stage kt-1
+        if (kt + GM_STAGES - 1 < KT) load(kt + GM_STAGES - 1, (kt + GM_STAGES - 1) % GM_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int stage = kt % GM_STAGES;
+        const bf16* as = As + (size_t)stage * GM_TM * GM_LD;
+        const bf16* bs = Bs + (size_t)stage * GM_TN * GM_LD;
+        const bf16* b2s = B2s + (size_t)stage * GM_TN * GM_LD;
+#pragma unroll
+        for (int kk = 0; kk < GM_TK; kk += 16) {
+            unsigned a[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+                ldmatrix_x4(a[mi], as + (size_t)(wm * 32 + mi * 16 + (lane & 15)) * GM_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {  // two n-tiles of 8 per ldmatrix
+                const size_t at = (size_t)(wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8) * GM_LD + kk + ((lane >> 3) & 1) * 8;
+                unsigned b[4];
+                ldmatrix_x4(b, bs + at);
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    mma_bf16(acc[mi][np * 2], a[mi], b[0], b[1]);
+                    mma_bf16(acc[mi][np * 2 + 1], a[mi], b[2], b[3]);
+                }
+                if (TWO) {
+                    ldmatrix_x4(b, b2s + at);
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi) {
+                        mma_bf16(acc2[TWO ? mi : 0][TWO ? np * 2 : 0], a[mi], b[0], b[1]);
+                        mma_bf16(acc2[TWO ? mi : 0][TWO ? np * 2 + 1 : 0], a[mi], b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int d = dst_s[wm * 32 + mi * 16 + half * 8 + (lane >> 2)];
+            if (d < 0) continue;
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + wn * 32 + ni * 8 + (lane & 3) * 2 + e;
+                    if (n >= Nout) continue;
+                    const size_t at = (size_t)d * ldc + (size_t)g * c_group_off + n;
+                    float v = acc[mi][ni][half * 2 + e];
+                    if (EPI == GG_EPI_STORE_F32) {
+                        ((float*)Cv)[at] = v;
+                    } else {
+                        if (TWO) v = v / (1.f + expf(-v)) * acc2[TWO ? mi : 0][TWO ? ni : 0][half * 2 + e];
+                        if (EPI == GG_EPI_SIGMOID_GATE)
+                            v = v / (1.f + expf(-to_f(gate[(size_t)d * ldg + (size_t)g * c_group_off + n])));
+                        ((bf16*)Cv)[at] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int EPI>
+static int launch_grouped_mma(dim3 grid, cudaStream_t stream, const void* A, int lda, int a_group_off, const void* B, const void* B2,
+                              long long b_stride, void* C, int ldc, int c_group_off, const int* offsets, const int* a_index,
+                              int a_div, const int* c_index, const void* gate, int ldg, int M, int Nout, int K, int G) {
+    const size_t smem = (size_t)GM_STAGES * (GM_TM + (EPI == GG_EPI_SILU_MUL ? 2 : 1) * GM_TN) * GM_LD * sizeof(bf16);
+    static bool configured = false;  // (per instantiation)
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_mma_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return cw_launch(grouped_gemm_mma_kernel<EPI>, grid, dim3(256), smem, stream, 1, (const bf16*)A, lda, a_group_off, (const bf16*)B,
+                     (const bf16*)B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, c_index, (const bf16*)gate, ldg, M, Nout,
+                     K, G);
+}
+
+static int g_grouped_mma = 1;
+extern "C" int cw_grouped_gemm_set_mma(int on) { g_grouped_mma = on ? 1 : 0; return CW_OK; }
+
 template <typename T>
 static int launch_grouped(int epi, dim3 grid, cudaStream_t stream, const void* A, int lda, int a_group_off, const void* B,
                           const void* B2, long long b_stride, void* C, int ldc, int c_group_off, const int* offsets,
@@ -160,6 +346,23 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
     if (dtype == 0)
         return launch_grouped<float>(epilogue, grid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets,
                                      a_index, a_div, c_index, gate, ldg, M, Nout, K, G);
+    const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_group_off % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 &&
+                         ((uintptr_t)B2 & 15) == 0;
+    if (dtype == 1 && g_grouped_mma && aligned) {
+        const long long mtiles = offsets == nullptr ? (long long)G * ((M + GM_TM - 1) / GM_TM) : (long long)(M + GM_TM - 1) / GM_TM + G;
+        dim3 mgrid((unsigned)mtiles, (Nout + GM_TN - 1) / GM_TN);
+#define GM_GO(E)                                                                                                                 \
+    return launch_grouped_mma<E>(mgrid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, \
+                                 c_index, gate, ldg, M, Nout, K, G)
+        switch (epilogue) {
+            case GG_EPI_STORE: GM_GO(GG_EPI_STORE);
+            case GG_EPI_STORE_F32: GM_GO(GG_EPI_STORE_F32);
+            case GG_EPI_SILU_MUL: GM_GO(GG_EPI_SILU_MUL);
+            case GG_EPI_SIGMOID_GATE: GM_GO(GG_EPI_SIGMOID_GATE);
+        }
+#undef GM_GO
+        return CW_ERR_UNSUPPORTED;
+    }
     if (dtype == 1)
         return launch_grouped<bf16>(epilogue, grid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets,
                                     a_index, a_div, c_index, gate, ldg, M, Nout, K, G);
@@ -170,7 +373,7 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
 // logits = Wr x + b in float32 (x as the run stores it); the `top` largest (the lower index wins a
 // tie); weights = softmax over the chosen logits.  sel < 0 marks a padding row.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ b,
                   const int* __restrict__ tok_seq, int* __restrict__ sel, float* __restrict__ wt, int W, int E, int top) {
     extern __shared__ float logit_s[];  // [E] logits, then [top] chosen logits
@@ -186,12 +389,21 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ Wr, const fl
         return;
     }
     const T* xr = x + (size_t)row * W;
-    for (int e = warp; e < E; e += 4) {
-        const float* w = Wr + (size_t)e * W;
-        float acc = 0.f;
-        for (int c = lane; c < W; c += 32) acc = fmaf(to_f(xr[c]), w[c], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) logit_s[e] = acc + (b != nullptr ? b[e] : 0.f);
+    const int warps = blockDim.x >> 5;
+    // a warp takes eight experts at a time: eight independent streams of router rows in flight, x read once
+    for (int e0 = warp * 8; e0 < E; e0 += warps * 8) {
+        float acc[8] = {};
+        for (int c = lane; c < W; c += 32) {
+            const float xv = to_f(xr[c]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (e0 + i < E) acc[i] = fmaf(xv, Wr[(size_t)(e0 + i) * W + c], acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float total = warp_sum(acc[i]);
+            if (lane == 0 && e0 + i < E) logit_s[e0 + i] = total + (b != nullptr ? b[e0 + i] : 0.f);
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -228,9 +440,9 @@ extern "C" int cw_moe_route(const void* x, const float* Wr, const float* b, cons
     if (E + top > 8192) return CW_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(E + top) * sizeof(float);
     if (dtype == 0)
-        return cw_launch(moe_route_kernel<float>, dim3(N), dim3(128), smem, stream, 1, (const float*)x, Wr, b, tok_seq, sel, wt, W, E, top);
+        return cw_launch(moe_route_kernel<float>, dim3(N), dim3(256), smem, stream, 1, (const float*)x, Wr, b, tok_seq, sel, wt, W, E, top);
     if (dtype == 1)
-        return cw_launch(moe_route_kernel<bf16>, dim3(N), dim3(128), smem, stream, 1, (const bf16*)x, Wr, b, tok_seq, sel, wt, W, E, top);
+        return cw_launch(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, 1, (const bf16*)x, Wr, b, tok_seq, sel, wt, W, E, top);
     return CW_ERR_BAD_DTYPE;
 }
 

@@ -144,10 +144,20 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
 //       a_i = exp(-exp(pre_i + p0_i));  y_j = sum_i q_i (S_ij + p1_i k_i v_j);  S_ij <- a_i S_ij + k_i v_j
 //   FORM 1 (one decay per head from a step size, output after the update, skip term):
 //       dt = softplus(pre + p0);  a = exp(-exp(p1) dt);  S_ij <- a S_ij + dt k_i v_j;  y_j = sum_i q_i S_ij + p2 v_j
-// q and k of head h are those of group h / heads_per_group.  A thread owns up to RS consecutive key
-// channels of one value column; the IP threads of a column are neighbouring lanes of a warp and sum up by
-// shuffles, so a token costs no block-wide barrier.  Blocks: (request, head, slice of value columns).
-#define RS 8
+// q and k of head h are those of group h / heads_per_group.  Blocks: (request, head, slice of value columns).
+#define RS 8    // key channels per thread
+#define RC 16   // tokens per staged chunk
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem) : "memory");
+}
+
+// The operands of RC tokens at a time are copied into shared memory (cp.async, the next chunk while the
+// current one is computed), turned into what the recurrence multiplies by (decays, step-scaled keys) once
+// per block, and read from there by the IP x JB threads; a thread owns key channels ipart, ipart + IP, ..
+// of value column j, so that neighbouring lanes read neighbouring words of shared memory and of the state.
+// The per-token sums over key channels are reduced over the IP lanes of a column after the chunk's loop.
 template <int FORM>
 __global__ void __launch_bounds__(128)
 recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
@@ -157,34 +167,34 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                        const long long* __restrict__ slots, const int* __restrict__ tok_seq,
                        const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP,
                        float* __restrict__ out, int ldo) {
+    extern __shared__ float rs_smem[];
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = blockIdx.x, h = blockIdx.y;
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int start = q_start[seq], end = q_start[seq + 1];
     if (end <= start) return;
-    const int ipart = threadIdx.x % IP, jl = threadIdx.x / IP, JB = blockDim.x / IP;
-    const int j = blockIdx.z * JB + jl;
+    const int ipart = tid % IP, jl = tid / IP, JB = blockDim.x / IP;
+    const int j0 = blockIdx.z * JB, j = j0 + jl;
     const bool live = j < Dv;
     if (tok_seq[start] < 0) {  // padding rows of a fixed-shape step: no request, no state
         if (live && ipart == 0)
             for (int t = start; t < end; ++t) out[(size_t)t * ldo + (size_t)h * Dv + j] = 0.f;
         return;
     }
-    const int R = (Dk + IP - 1) / IP;
-    const int i0 = ipart * R;
+    // one buffer: q [RC][Dk], k [RC][Dk], a [RC][Dk] (FORM 0) or a, dt [2][RC] (FORM 1), v [RC][JB]
+    const int a_words = FORM == 0 ? RC * Dk : 2 * RC;
+    const int buf_words = 2 * RC * Dk + a_words + RC * JB;
     const int g = h / heads_per_group;
     float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
     float S[RS], c0[RS], c1[RS];
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
-        const int i = i0 + r;
-        const bool on = r < R && i < Dk;
+        const int i = ipart + r * IP;
+        const bool on = i < Dk;
         S[r] = (on && live) ? S_mem[i] : 0.f;
-        if (FORM == 0) {
-            c0[r] = on ? p0[(size_t)h * Dk + i] : 0.f;
-            c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
-        }
+        if (FORM == 0) c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
     }
+    (void)c0;
     float head_p0 = 0.f, head_decay = 0.f, head_skip = 0.f;
     if (FORM == 1) {
         head_p0 = p0[h];
@@ -194,59 +204,95 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     const float* qp = q + (size_t)g * Dk;
     const float* kp = k + (size_t)g * Dk;
     const float* pp = FORM == 0 ? pre + (size_t)h * Dk : pre + h;
-    const float* vp = v + (size_t)h * Dv + (live ? j : 0);
-    float qn[RS], kn[RS], an[RS], vn, dn = 0.f;
-    // the next token's operands are fetched while the current one is computed
-    auto fetch = [&](int t) {
-#pragma unroll
-        for (int r = 0; r < RS; ++r) {
-            const int i = i0 + r;
-            const bool on = r < R && i < Dk;
-            qn[r] = on ? qp[(size_t)t * ldq + i] : 0.f;
-            kn[r] = on ? kp[(size_t)t * ldk + i] : 0.f;
-            if (FORM == 0) an[r] = on ? pp[(size_t)t * ldp + i] : 0.f;
+    const float* vp = v + (size_t)h * Dv + j0;
+    const int nv = min(JB, Dv - j0);
+    auto fetch = [&](int t0, float* buf) {  // raw operands of tokens t0 .. t0+RC-1 (those below `end`)
+        const int n = min(RC, end - t0);
+        float* qs = buf;
+        float* ks = buf + RC * Dk;
+        float* as = buf + 2 * RC * Dk;
+        float* vs = as + a_words;
+        for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
+            const int t = idx / Dk, i = idx - t * Dk;
+            cp_async4(qs + idx, qp + (size_t)(t0 + t) * ldq + i);
+            cp_async4(ks + idx, kp + (size_t)(t0 + t) * ldk + i);
+            if (FORM == 0) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
         }
-        if (FORM == 1) dn = pp[(size_t)t * ldp];
-        vn = vp[(size_t)t * ldv];
+        if (FORM == 1)
+            for (int t = tid; t < n; t += blockDim.x) cp_async4(as + t, pp + (size_t)(t0 + t) * ldp);
+        for (int idx = tid; idx < n * nv; idx += blockDim.x) {
+            const int t = idx / nv, c = idx - t * nv;
+            cp_async4(vs + t * JB + c, vp + (size_t)(t0 + t) * ldv + c);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch(start);
-    for (int t = start; t < end; ++t) {
-        float qc[RS], kc[RS], ac[RS];
-        const float vc = vn, dc = dn;
-#pragma unroll
-        for (int r = 0; r < RS; ++r) {
-            qc[r] = qn[r];
-            kc[r] = kn[r];
-            if (FORM == 0) ac[r] = an[r];
-        }
-        if (t + 1 < end) fetch(t + 1);
-        float part = 0.f;
+    fetch(start, rs_smem);
+    int which = 0;
+    for (int t0 = start; t0 < end; t0 += RC, which ^= 1) {
+        const int n = min(RC, end - t0);
+        float* buf = rs_smem + which * buf_words;
+        float* qs = buf;
+        float* ks = buf + RC * Dk;
+        float* as = buf + 2 * RC * Dk;
+        float* vs = as + a_words;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // this chunk has landed; everyone has left the other buffer
+        if (t0 + RC < end) fetch(t0 + RC, rs_smem + (which ^ 1) * buf_words);
         if (FORM == 0) {
-#pragma unroll
-            for (int r = 0; r < RS; ++r) {
-                const float a = expf(-expf(ac[r] + c0[r]));
-                const float kv = kc[r] * vc;
-                part = fmaf(qc[r], fmaf(c1[r], kv, S[r]), part);
-                S[r] = fmaf(a, S[r], kv);
+            for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
+                const int i = idx % Dk;
+                as[idx] = expf(-expf(as[idx] + p0[(size_t)h * Dk + i]));
             }
         } else {
-            const float x = dc + head_p0;
-            const float dt = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // softplus without a threshold
-            const float a = expf(-head_decay * dt);
+            if (tid < n) {
+                const float x = as[tid] + head_p0;
+                const float dt = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // softplus without a threshold
+                as[RC + tid] = dt;
+                as[tid] = expf(-head_decay * dt);
+            }
+            __syncthreads();
+            for (int idx = tid; idx < n * Dk; idx += blockDim.x) ks[idx] *= as[RC + idx / Dk];
+        }
+        __syncthreads();
+        float part[RC];
 #pragma unroll
-            for (int r = 0; r < RS; ++r) {
-                S[r] = fmaf(a, S[r], dt * kc[r] * vc);
-                part = fmaf(qc[r], S[r], part);
+        for (int t = 0; t < RC; ++t) {
+            part[t] = 0.f;
+            if (t < n) {
+                const float vc = live ? vs[t * JB + jl] : 0.f;
+                const float a1 = FORM == 1 ? as[t] : 0.f;
+                float sum = 0.f;
+#pragma unroll
+                for (int r = 0; r < RS; ++r) {
+                    const int i = ipart + r * IP;
+                    if (i < Dk) {
+                        const float kv = ks[t * Dk + i] * vc, qc = qs[t * Dk + i];
+                        if (FORM == 0) {
+                            sum = fmaf(qc, fmaf(c1[r], kv, S[r]), sum);
+                            S[r] = fmaf(as[t * Dk + i], S[r], kv);
+                        } else {
+                            S[r] = fmaf(a1, S[r], kv);
+                            sum = fmaf(qc, S[r], sum);
+                        }
+                    }
+                }
+                part[t] = sum;
             }
         }
-        for (int o = 1; o < IP; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        if (live && ipart == 0) out[(size_t)t * ldo + (size_t)h * Dv + j] = FORM == 1 ? fmaf(head_skip, vc, part) : part;
+#pragma unroll
+        for (int t = 0; t < RC; ++t)
+            for (int o = 1; o < IP; o <<= 1) part[t] += __shfl_xor_sync(0xffffffffu, part[t], o);
+        if (live && ipart == 0) {
+#pragma unroll
+            for (int t = 0; t < RC; ++t)
+                if (t < n) out[(size_t)(t0 + t) * ldo + (size_t)h * Dv + j] = FORM == 1 ? fmaf(head_skip, vs[t * JB + jl], part[t]) : part[t];
+        }
     }
     if (live) {
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
-            const int i = i0 + r;
-            if (r < R && i < Dk) S_mem[i] = S[r];
+            const int i = ipart + r * IP;
+            if (i < Dk) S_mem[i] = S[r];
         }
     }
 }
@@ -263,60 +309,70 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     while (IP * RS < Dk) IP *= 2;
     const int JB = 128 / IP;
     dim3 grid(S, H, (Dv + JB - 1) / JB);
+    const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (form == 0 ? RC * Dk : 2 * RC) + RC * JB);
+    static size_t allowed[2] = {48 << 10, 48 << 10};
+    if (form != 0 && form != 1) return CW_ERR_UNSUPPORTED;
+    if (smem > allowed[form]) {
+        const cudaError_t e = form == 0 ? cudaFuncSetAttribute(recurrence_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                        : cudaFuncSetAttribute(recurrence_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed[form] = smem;
+    }
     if (form == 0)
-        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(128), 0, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(128), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
                          state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
-    if (form == 1)
-        return cw_launch(recurrence_scan_kernel<1>, grid, dim3(128), 0, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
-    return CW_ERR_UNSUPPORTED;
+    return cw_launch(recurrence_scan_kernel<1>, grid, dim3(128), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
 }
 
 // ---- gated norm in parts ----------------------------------------------------------------------------
 // y [N, C] float32, gate z [N, ldz] float32.  gate_first: u = y silu(z), out = u / rms_part(u) * weight.
-// Otherwise: out = y / rms_part(y) * weight * silu(z).  A warp per part.
+// Otherwise: out = y / rms_part(y) * weight * silu(z).  A block per (row, part); sums in a fixed order.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ weight,
                         T* __restrict__ out, int C, int parts, float eps, int gate_first) {
+    __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int row = blockIdx.x, p = blockIdx.y;
     const int width = C / parts;
-    for (int p = warp; p < parts; p += warps) {
-        const float* yr = y + (size_t)row * C + (size_t)p * width;
-        const float* zr = z + (size_t)row * ldz + (size_t)p * width;
-        float ss = 0.f;
-        for (int c = lane; c < width; c += 32) {
-            float u = yr[c];
-            if (gate_first) {
-                const float g = zr[c];
-                u *= g / (1.f + expf(-g));
-            }
-            ss = fmaf(u, u, ss);
-        }
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-        for (int c = lane; c < width; c += 32) {
+    const float* yr = y + (size_t)row * C + (size_t)p * width;
+    const float* zr = z + (size_t)row * ldz + (size_t)p * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float u = yr[c];
+        if (gate_first) {
             const float g = zr[c];
-            const float sg = g / (1.f + expf(-g));
-            const float u = gate_first ? yr[c] * sg : yr[c];
-            float r = u * inv * weight[(size_t)p * width + c];
-            if (!gate_first) r *= sg;
-            out[(size_t)row * C + (size_t)p * width + c] = from_f<T>(r);
+            u *= g / (1.f + expf(-g));
         }
+        ss = fmaf(u, u, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float g = zr[c];
+        const float sg = g / (1.f + expf(-g));
+        const float u = gate_first ? yr[c] * sg : yr[c];
+        float r = u * inv * weight[(size_t)p * width + c];
+        if (!gate_first) r *= sg;
+        out[(size_t)row * C + (size_t)p * width + c] = from_f<T>(r);
     }
 }
 
 extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, const float* weight, void* out, int N, int C,
                                    int parts, float eps, int gate_first, int dtype, cudaStream_t stream) {
     if (N == 0) return CW_OK;
-    if (N < 0 || C <= 0 || parts <= 0 || C % parts || ldz < C) return CW_ERR_BAD_SIZE;
+    if (N < 0 || C <= 0 || parts <= 0 || C % parts || ldz < C || parts > 65535) return CW_ERR_BAD_SIZE;
+    const int width = C / parts;
+    int threads = 32;
+    while (threads < 256 && threads * 4 < width) threads *= 2;
+    dim3 grid(N, parts);
     if (dtype == 0)
-        return cw_launch(gated_group_norm_kernel<float>, dim3(N), dim3(128), 0, stream, 1, y, z, ldz, weight, (float*)out, C, parts,
+        return cw_launch(gated_group_norm_kernel<float>, grid, dim3(threads), 0, stream, 1, y, z, ldz, weight, (float*)out, C, parts,
                          eps, gate_first);
     if (dtype == 1)
-        return cw_launch(gated_group_norm_kernel<bf16>, dim3(N), dim3(128), 0, stream, 1, y, z, ldz, weight, (bf16*)out, C, parts,
+        return cw_launch(gated_group_norm_kernel<bf16>, grid, dim3(threads), 0, stream, 1, y, z, ldz, weight, (bf16*)out, C, parts,
                          eps, gate_first);
     return CW_ERR_BAD_DTYPE;
 }

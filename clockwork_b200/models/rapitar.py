@@ -43,9 +43,33 @@ class RapitarConfig:
     raw: dict
 
 
+def _layers_2k(repeats: int) -> list:
+    """Layer sizes of published models of about 2,048 width: a time-mixing layer of 32 heads of 64, latent attention
+    of 16 heads over a latent of 512 + 64, a state-space layer of 64 heads of 64 with 128 states; dense feed-forwards
+    of 3.5 widths and 64 experts of 1,408 of which 6 are chosen."""
+    dense = {"kind": "dense", "ff": 7168}
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 64, "top": 6}}
+    wkv = {"type": "wkv", "mixer": {"heads": 32, "dim": 64, "decay_rank": 64}, "mlp": dense}
+    latent = {"type": "latent_attention", "mlp": moe,
+              "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536,
+                        "rot": {"base": 10000.0, "dims": 64}, "scale": 192 ** -0.5}}
+    mamba = {"heads": 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    return [wkv, latent, {"type": "mamba2", "mixer": mamba, "mlp": moe}, {"type": "mamba2", "mixer": mamba, "mlp": dense}] * repeats
+
+
 class RapitarArchitecture:
     name = "Rapitar"
     layer_count_key = None  # the layers are a list: a shape with fewer layers is another list
+    # config.json contents of the sizes that the benchmarks and the command line know by name
+    named_shapes = {
+        "rapitar-2k": {"architecture": "Rapitar", "vocab": 32768, "width": 2048, "norm": {"eps": 1e-6}, "layers": _layers_2k(2)},
+        "rapitar-tiny": {"architecture": "Rapitar", "vocab": 256, "width": 64, "norm": {"eps": 1e-6}, "layers": [
+            {"type": "wkv", "mixer": {"heads": 2, "dim": 16, "decay_rank": 8}, "mlp": {"kind": "dense", "ff": 96}},
+            {"type": "latent_attention", "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 4, "top": 2}},
+             "mixer": {"heads": 2, "dim": 16, "rot_dim": 8, "vdim": 16, "kv_rank": 24, "q_rank": 16,
+                       "rot": {"base": 10000.0, "dims": 8}, "scale": 0.2}},
+            {"type": "mamba2", "mixer": {"heads": 2, "vdim": 16, "state": 8, "groups": 1, "conv": 4, "norm_groups": 1}, "mlp": None}]},
+    }
 
     @staticmethod
     def _mixer(kind: str, m: dict[str, Any], width: int, eps: float, where: str) -> PartSpec:

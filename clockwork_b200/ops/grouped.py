@@ -10,6 +10,12 @@ from .library import check, library
 EPI_STORE, EPI_STORE_F32, EPI_SILU_MUL, EPI_SIGMOID_GATE = 0, 1, 2, 3
 
 
+def set_tensor_cores(on: bool) -> None:
+    """bfloat16 products in groups run on the tensor cores when their sizes allow (the default); ``False`` keeps them
+    on the CUDA-core kernel that float32 runs use (for comparisons)."""
+    library().cw_grouped_gemm_set_mma(1 if on else 0)
+
+
 def per_head_product(a: torch.Tensor, a_head_width: int, w: torch.Tensor, out: torch.Tensor, out_head_width: int,
                      gate: torch.Tensor | None = None) -> torch.Tensor:
     """For every head h: ``out[:, h*out_head_width : +n] = a[:, h*a_head_width : +k] @ w[h].T`` with ``w`` [H, n, k];

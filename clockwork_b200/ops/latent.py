@@ -8,6 +8,12 @@ from . import _need, _ptr, _stream, dtype_code
 from .library import check, library
 
 
+def set_tensor_cores(on: bool) -> None:
+    """bfloat16 attention over the latent runs on the tensor cores when its sizes allow (the default); ``False`` keeps
+    it on the CUDA-core kernel that float32 runs use (for comparisons)."""
+    library().cw_latent_attention_set_mma(1 if on else 0)
+
+
 def latent_prepare(down: torch.Tensor, q: torch.Tensor, qa: torch.Tensor, view, norm_weight: torch.Tensor,
                    inv_freq: torch.Tensor, positions: torch.Tensor, heads: int, dim: int, rot: int, rank: int, eps: float,
                    status: torch.Tensor) -> None:

@@ -334,3 +334,72 @@ def test_dense_feed_forward_and_offset_norm_alone():
     stream = ResidualStream(x.to(DEV).contiguous())
     got = norm.forward(stream, harness.status)
     assert float((got.cpu().double() - plain.offset_norm(x.double(), g.double(), 1e-3)).abs().max()) < 1e-5
+
+
+# ---- the tensor-core forms of the bfloat16 kernels against the CUDA-core forms ---------------------------
+
+def bf16_mixer_both_ways(part, x, portions, toggle, page_size=16):
+    outs = []
+    for on in (True, False):
+        toggle(on)
+        try:
+            outs.append(run_mixer(part, x, portions, page_size=page_size))
+        finally:
+            toggle(True)
+    return outs
+
+
+@pytest.mark.parametrize("heads, rank, rot", [(16, 64, 16), (20, 136, 8), (3, 512, 64)])
+def test_latent_attention_on_tensor_cores(heads, rank, rot):
+    from clockwork_b200.ops import latent as latent_ops
+
+    gen = torch.Generator().manual_seed(heads)
+    w, dim, vdim, q_rank = 64, 16, 24, 32
+    t = {"m.dq": draw(gen, (q_rank, w), 0.3), "m.dq.norm": draw(gen, (q_rank,), 0.2, 1.0), "m.uq": draw(gen, (heads * (dim + rot), q_rank), 1.0),
+         "m.dkv": draw(gen, (rank + rot, w), 0.6), "m.dkv.norm": draw(gen, (rank,), 0.2, 1.0), "m.uk": draw(gen, (heads * dim, rank), 0.3),
+         "m.uv": draw(gen, (heads * vdim, rank), 0.2), "m.sink": draw(gen, (heads,), 1.5, 2.0), "m.g": draw(gen, (heads * vdim, w), 0.3),
+         "m.o": draw(gen, (w, heads * vdim), 0.2)}
+    cfg = dict(heads=heads, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=rank, q_rank=q_rank, scale=0.35, rot={"base": 300.0, "dims": rot})
+    spec = PartSpec("latent_attention", dict(hidden_size=w, heads=heads, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=rank, q_rank=q_rank,
+                                             scale=0.35, rope_base=300.0, eps=1e-5))
+    part = part_with_weights("mixer", spec, "m", torch.bfloat16, t)
+    x = draw(gen, (200, w))
+    wd = {k: v.double() for k, v in t.items()}
+    want = plain.latent_attention_mixer(x.double(), wd, "m", cfg, 1e-5)
+    yard = float((plain.latent_attention_mixer(x.double(), wd, "m", cfg, 1e-5, rnd=plain.to_bfloat16_and_back) - want).abs().max())
+    for portions in ([200], [63, 1, 1, 2, 64, 69]):
+        fast, slow = bf16_mixer_both_ways(part, x, portions, latent_ops.set_tensor_cores)
+        assert float((fast.double() - want).abs().max()) <= 3 * yard, portions
+        assert float((slow.double() - want).abs().max()) <= 3 * yard, portions
+        assert float((fast - slow).abs().max()) <= yard, portions
+
+
+@pytest.mark.parametrize("experts, top, ff, w, n", [(7, 3, 136, 256, 300), (64, 6, 64, 128, 9), (5, 5, 40, 64, 130)])
+def test_products_in_groups_on_tensor_cores(experts, top, ff, w, n):
+    from clockwork_b200.ops import grouped as grouped_ops
+
+    gen = torch.Generator().manual_seed(experts)
+    t = {"f.router": draw(gen, (experts, w), 0.6), "f.router.b": draw(gen, (experts,), 0.3)}
+    for e in range(experts):
+        t.update({f"f.e{e}.gate": draw(gen, (ff, w), 0.2), f"f.e{e}.up": draw(gen, (ff, w), 0.2), f"f.e{e}.down": draw(gen, (w, ff), 0.2)})
+    part = part_with_weights("ffn", PartSpec("moe", dict(hidden_size=w, expert_size=ff, experts=experts, top=top)), "f", torch.bfloat16, t)
+    x = draw(gen, (n, w))
+    cfg = {"router": {"experts": experts, "top": top}}
+    wd = {k: v.double() for k, v in t.items()}
+    want = plain.routed_ff(x.double(), wd, "f", cfg)
+    yard = float((plain.routed_ff(x.double(), wd, "f", cfg, rnd=plain.to_bfloat16_and_back) - want).abs().max())
+    harness = PartHarness({}, torch.bfloat16)
+    outs = []
+    for on in (True, False):
+        grouped_ops.set_tensor_cores(on)
+        try:
+            prepared = harness.prepare({f"r{on}": n})
+            stream = ResidualStream(torch.zeros((n, w), dtype=torch.float32, device=DEV))
+            stream.push(part.forward(prepared.ctx, x.to(DEV, torch.bfloat16).contiguous(), stream))
+            stream.flush()
+            outs.append(stream.residual.cpu())
+        finally:
+            grouped_ops.set_tensor_cores(True)
+    for got in outs:
+        assert float((got.double() - want).abs().max()) <= 3 * yard
+    assert float((outs[0] - outs[1]).abs().max()) <= yard
