@@ -370,43 +370,29 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
 }
 
 // ---- router ---------------------------------------------------------------------------------------
-// logits = Wr x + b in float32 (x as the run stores it); the `top` largest (the lower index wins a
-// tie); weights = softmax over the chosen logits.  sel < 0 marks a padding row.
-template <typename T>
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ b,
-                  const int* __restrict__ tok_seq, int* __restrict__ sel, float* __restrict__ wt, int W, int E, int top) {
-    extern __shared__ float logit_s[];  // [E] logits, then [top] chosen logits
-    float* chosen_s = logit_s + E;
+// logits [N, E] float32 (a product with float32 accumulation, made by the caller) + bias; the `top`
+// largest (the lower index wins a tie); weights = softmax over the chosen logits.  sel < 0 marks a
+// padding row.  A warp per token.
+__global__ void __launch_bounds__(128)
+moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b, const int* __restrict__ tok_seq,
+                  int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top) {
+    extern __shared__ float choose_s[];  // per warp: [E] logits, then [top] chosen logits
     pdl_launch_dependents();
     pdl_wait();
-    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= N) return;
     if (tok_seq[row] < 0) {
-        for (int t = threadIdx.x; t < top; t += blockDim.x) {
+        for (int t = lane; t < top; t += 32) {
             sel[(size_t)row * top + t] = -1;
             wt[(size_t)row * top + t] = 0.f;
         }
         return;
     }
-    const T* xr = x + (size_t)row * W;
-    const int warps = blockDim.x >> 5;
-    // a warp takes eight experts at a time: eight independent streams of router rows in flight, x read once
-    for (int e0 = warp * 8; e0 < E; e0 += warps * 8) {
-        float acc[8] = {};
-        for (int c = lane; c < W; c += 32) {
-            const float xv = to_f(xr[c]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (e0 + i < E) acc[i] = fmaf(xv, Wr[(size_t)(e0 + i) * W + c], acc[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float total = warp_sum(acc[i]);
-            if (lane == 0 && e0 + i < E) logit_s[e0 + i] = total + (b != nullptr ? b[e0 + i] : 0.f);
-        }
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    float* logit_s = choose_s + (size_t)warp * (E + top);
+    float* chosen_s = logit_s + E;
+    for (int e = lane; e < E; e += 32) logit_s[e] = logits[(size_t)row * E + e] + (b != nullptr ? b[e] : 0.f);
+    __syncwarp();
     for (int t = 0; t < top; ++t) {
         float best = -INFINITY;
         int at = 0x7fffffff;
@@ -433,17 +419,13 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ Wr, const fl
     for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = expf(chosen_s[t] - first) / total;
 }
 
-extern "C" int cw_moe_route(const void* x, const float* Wr, const float* b, const int* tok_seq, int* sel, float* wt, int N,
-                            int W, int E, int top, int dtype, cudaStream_t stream) {
+extern "C" int cw_moe_choose(const float* logits, const float* b, const int* tok_seq, int* sel, float* wt, int N, int E, int top,
+                             cudaStream_t stream) {
     if (N == 0) return CW_OK;
-    if (N < 0 || W <= 0 || E <= 0 || top <= 0 || top > E) return CW_ERR_BAD_SIZE;
-    if (E + top > 8192) return CW_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(E + top) * sizeof(float);
-    if (dtype == 0)
-        return cw_launch(moe_route_kernel<float>, dim3(N), dim3(256), smem, stream, 1, (const float*)x, Wr, b, tok_seq, sel, wt, W, E, top);
-    if (dtype == 1)
-        return cw_launch(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, 1, (const bf16*)x, Wr, b, tok_seq, sel, wt, W, E, top);
-    return CW_ERR_BAD_DTYPE;
+    if (N < 0 || E <= 0 || top <= 0 || top > E) return CW_ERR_BAD_SIZE;
+    const size_t smem = 4 * (size_t)(E + top) * sizeof(float);
+    if (smem > (48 << 10)) return CW_ERR_UNSUPPORTED;
+    return cw_launch(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, 1, logits, b, tok_seq, sel, wt, N, E, top);
 }
 
 // ---- pairs by expert --------------------------------------------------------------------------------

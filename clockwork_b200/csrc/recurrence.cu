@@ -148,6 +148,10 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
 #define RS 8    // key channels per thread
 #define RC 16   // tokens per staged chunk
 
+__device__ __forceinline__ void cp_async16f(float* smem, const float* gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem) : "memory");
@@ -159,15 +163,15 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 // of value column j, so that neighbouring lanes read neighbouring words of shared memory and of the state.
 // The per-token sums over key channels are reduced over the IP lanes of a column after the chunk's loop.
 template <int FORM>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                        const float* __restrict__ v, int ldv, const float* __restrict__ pre, int ldp,
                        const float* __restrict__ p0, const float* __restrict__ p1, const float* __restrict__ p2,
                        float* __restrict__ state, long long state_stride, long long state_off,
                        const long long* __restrict__ slots, const int* __restrict__ tok_seq,
-                       const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP,
+                       const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP, int wide,
                        float* __restrict__ out, int ldo) {
-    extern __shared__ float rs_smem[];
+    extern __shared__ __align__(16) float rs_smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -212,11 +216,21 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         float* ks = buf + RC * Dk;
         float* as = buf + 2 * RC * Dk;
         float* vs = as + a_words;
-        for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
-            const int t = idx / Dk, i = idx - t * Dk;
-            cp_async4(qs + idx, qp + (size_t)(t0 + t) * ldq + i);
-            cp_async4(ks + idx, kp + (size_t)(t0 + t) * ldk + i);
-            if (FORM == 0) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
+        if (wide) {  // rows of whole 16-byte pieces at 16-byte addresses
+            const int pieces = Dk >> 2;
+            for (int idx = tid; idx < n * pieces; idx += blockDim.x) {
+                const int t = idx / pieces, i = (idx - t * pieces) << 2;
+                cp_async16f(qs + t * Dk + i, qp + (size_t)(t0 + t) * ldq + i);
+                cp_async16f(ks + t * Dk + i, kp + (size_t)(t0 + t) * ldk + i);
+                if (FORM == 0) cp_async16f(as + t * Dk + i, pp + (size_t)(t0 + t) * ldp + i);
+            }
+        } else {
+            for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
+                const int t = idx / Dk, i = idx - t * Dk;
+                cp_async4(qs + idx, qp + (size_t)(t0 + t) * ldq + i);
+                cp_async4(ks + idx, kp + (size_t)(t0 + t) * ldk + i);
+                if (FORM == 0) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
+            }
         }
         if (FORM == 1)
             for (int t = tid; t < n; t += blockDim.x) cp_async4(as + t, pp + (size_t)(t0 + t) * ldp);
@@ -307,8 +321,12 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     if (Dk > 32 * RS || H > 65535) return CW_ERR_UNSUPPORTED;
     int IP = 1;
     while (IP * RS < Dk) IP *= 2;
-    const int JB = 128 / IP;
+    int threads = 256;  // more value columns per block share the staged q and k; fewer when a head has few columns
+    while (threads > 32 && threads / IP >= 2 * Dv) threads /= 2;
+    const int JB = threads / IP;
     dim3 grid(S, H, (Dv + JB - 1) / JB);
+    const int wide = Dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (form == 1 || ldp % 4 == 0) && ((uintptr_t)q & 15) == 0 &&
+                     ((uintptr_t)k & 15) == 0 && (form == 1 || ((uintptr_t)pre & 15) == 0);
     const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (form == 0 ? RC * Dk : 2 * RC) + RC * JB);
     static size_t allowed[2] = {48 << 10, 48 << 10};
     if (form != 0 && form != 1) return CW_ERR_UNSUPPORTED;
@@ -319,10 +337,10 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
         allowed[form] = smem;
     }
     if (form == 0)
-        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(128), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
-    return cw_launch(recurrence_scan_kernel<1>, grid, dim3(128), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, out, ldo);
+        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, out, ldo);
+    return cw_launch(recurrence_scan_kernel<1>, grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, out, ldo);
 }
 
 // ---- gated norm in parts ----------------------------------------------------------------------------

@@ -34,15 +34,14 @@ def per_head_product(a: torch.Tensor, a_head_width: int, w: torch.Tensor, out: t
     return out
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, tok_seq: torch.Tensor, top: int):
-    """(chosen experts int32 [N, top], their weights float32 [N, top]); padding rows choose -1."""
-    _need(x, None, "x", 2)
-    _need(router, torch.float32, "router", 2)
-    n, w = x.shape
-    sel = torch.empty((n, top), dtype=torch.int32, device=x.device)
-    wt = torch.empty((n, top), dtype=torch.float32, device=x.device)
-    check(library().cw_moe_route(_ptr(x), _ptr(router), _ptr(bias), _ptr(tok_seq), _ptr(sel), _ptr(wt), n, w, router.shape[0], top,
-                                 dtype_code(x.dtype), _stream()), "moe_route")
+def moe_choose(logits: torch.Tensor, bias: torch.Tensor | None, tok_seq: torch.Tensor, top: int):
+    """(chosen experts int32 [N, top], their weights float32 [N, top]) from float32 router logits [N, E] (+ bias): the
+    ``top`` largest, weighted by the softmax over the chosen ones; padding rows choose -1."""
+    _need(logits, torch.float32, "logits", 2)
+    n, e = logits.shape
+    sel = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(library().cw_moe_choose(_ptr(logits), _ptr(bias), _ptr(tok_seq), _ptr(sel), _ptr(wt), n, e, top, _stream()), "moe_choose")
     return sel, wt
 
 

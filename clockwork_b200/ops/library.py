@@ -41,7 +41,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, I, P],
     "cw_grouped_gemm_set_mma": [I],
     "cw_latent_attention_set_mma": [I],
-    "cw_moe_route": [P, P, P, P, P, P, I, I, I, I, I, P],
+    "cw_moe_choose": [P, P, P, P, P, I, I, I, P],
     "cw_moe_group": [P, P, P, P, I, I, P],
     "cw_moe_combine": [P, P, P, P, I, I, I, P],
     # attention over a cached latent (csrc/latent_attention.cu)

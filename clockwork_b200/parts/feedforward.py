@@ -4,7 +4,8 @@
 tensors ``up`` [I, H], ``down`` [H, I].
 
 ``moe``: ``experts`` SwiGLU experts without biases (``e<i>.gate``, ``e<i>.up`` [F, H], ``e<i>.down``
-[H, F]), a router ``router`` [E, H] with bias ``router.b``.  Router logits are float32; each token takes
+[H, F]), a router ``router`` [E, H] with bias ``router.b``.  Router logits are a product with float32
+accumulation and stay float32; each token takes
 the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; the
 output is the weighted sum of the chosen experts' outputs, added into the float32 residual in the order
 of the choices.  Tokens are grouped by expert on the device (no host round trip), so the part is safe
@@ -68,17 +69,17 @@ class MixtureOfExperts(FeedForward):
             yield TensorDecl(self.name(f"e{e}.gate"), (f, h), "matrix", "linear")
             yield TensorDecl(self.name(f"e{e}.up"), (f, h), "matrix", "linear")
             yield TensorDecl(self.name(f"e{e}.down"), (h, f), "matrix", "linear")
-        yield TensorDecl(self.name("router"), (self.experts, h), "vector", "linear")  # kept in float32
+        yield TensorDecl(self.name("router"), (self.experts, h), "matrix", "linear")
         yield TensorDecl(self.name("router.b"), (self.experts,), "vector", "bias")
 
     def load_weights(self, fetch) -> None:
         stack = lambda what: torch.stack([fetch(self.name(f"e{e}.{what}")) for e in range(self.experts)]).contiguous()  # noqa: E731
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
-        self.router = fetch(self.name("router"))
+        self.router = Linear(fetch(self.name("router")))
         self.router_bias = fetch(self.name("router.b"))
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):
-        sel, weights = grouped_ops.moe_route(x, self.router, self.router_bias, ctx.tok_seq, self.top)
+        sel, weights = grouped_ops.moe_choose(self.router.to_float32(x), self.router_bias, ctx.tok_seq, self.top)
         offsets, order = grouped_ops.moe_group(sel, self.experts)
         act = grouped_ops.expert_gate_up(x, self.w_gate, self.w_up, offsets, order, self.top)
         y = grouped_ops.expert_down(act, self.w_down, offsets, order)
