@@ -162,7 +162,7 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 // per block, and read from there by the IP x JB threads; a thread owns key channels ipart, ipart + IP, ..
 // of value column j, so that neighbouring lanes read neighbouring words of shared memory and of the state.
 // The per-token sums over key channels are reduced over the IP lanes of a column after the chunk's loop.
-template <int FORM>
+template <int FORM, bool VEC>
 __global__ void __launch_bounds__(256)
 recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                        const float* __restrict__ v, int ldv, const float* __restrict__ pre, int ldp,
@@ -190,15 +190,17 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     const int buf_words = 2 * RC * Dk + a_words + RC * JB;
     const int g = h / heads_per_group;
     float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
-    float S[RS], c0[RS], c1[RS];
+    // VEC (Dk == 8 IP): a thread owns the eight consecutive channels 8 ipart .., read as two 16-byte words per
+    // operand and token; otherwise channels ipart, ipart + IP, .. one word at a time
+    const int i_first = VEC ? ipart * RS : ipart, i_step = VEC ? 1 : IP;
+    float S[RS], c1[RS];
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
-        const int i = ipart + r * IP;
+        const int i = i_first + r * i_step;
         const bool on = i < Dk;
         S[r] = (on && live) ? S_mem[i] : 0.f;
         if (FORM == 0) c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
     }
-    (void)c0;
     float head_p0 = 0.f, head_decay = 0.f, head_skip = 0.f;
     if (FORM == 1) {
         head_p0 = p0[h];
@@ -276,17 +278,44 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                 const float vc = live ? vs[t * JB + jl] : 0.f;
                 const float a1 = FORM == 1 ? as[t] : 0.f;
                 float sum = 0.f;
+                if (VEC) {
+                    const int at = t * Dk + i_first;
+                    float kc[RS], qc[RS], ac[RS];
+                    *(float4*)&kc[0] = *(const float4*)(ks + at);
+                    *(float4*)&kc[4] = *(const float4*)(ks + at + 4);
+                    *(float4*)&qc[0] = *(const float4*)(qs + at);
+                    *(float4*)&qc[4] = *(const float4*)(qs + at + 4);
+                    if (FORM == 0) {
+                        *(float4*)&ac[0] = *(const float4*)(as + at);
+                        *(float4*)&ac[4] = *(const float4*)(as + at + 4);
+                    }
+                    float sum2 = 0.f;  // two chains of four, added at the end: the same order for every token and batch
 #pragma unroll
-                for (int r = 0; r < RS; ++r) {
-                    const int i = ipart + r * IP;
-                    if (i < Dk) {
-                        const float kv = ks[t * Dk + i] * vc, qc = qs[t * Dk + i];
+                    for (int r = 0; r < RS; ++r) {
+                        const float kv = kc[r] * vc;
+                        float& acc_sum = r < 4 ? sum : sum2;
                         if (FORM == 0) {
-                            sum = fmaf(qc, fmaf(c1[r], kv, S[r]), sum);
-                            S[r] = fmaf(as[t * Dk + i], S[r], kv);
+                            acc_sum = fmaf(qc[r], fmaf(c1[r], kv, S[r]), acc_sum);
+                            S[r] = fmaf(ac[r], S[r], kv);
                         } else {
                             S[r] = fmaf(a1, S[r], kv);
-                            sum = fmaf(qc, S[r], sum);
+                            acc_sum = fmaf(qc[r], S[r], acc_sum);
+                        }
+                    }
+                    sum += sum2;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < RS; ++r) {
+                        const int i = ipart + r * IP;
+                        if (i < Dk) {
+                            const float kv = ks[t * Dk + i] * vc, qc = qs[t * Dk + i];
+                            if (FORM == 0) {
+                                sum = fmaf(qc, fmaf(c1[r], kv, S[r]), sum);
+                                S[r] = fmaf(as[t * Dk + i], S[r], kv);
+                            } else {
+                                S[r] = fmaf(a1, S[r], kv);
+                                sum = fmaf(qc, S[r], sum);
+                            }
                         }
                     }
                 }
@@ -305,7 +334,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     if (live) {
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
-            const int i = ipart + r * IP;
+            const int i = i_first + r * i_step;
             if (i < Dk) S_mem[i] = S[r];
         }
     }
@@ -328,18 +357,21 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     const int wide = Dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (form == 1 || ldp % 4 == 0) && ((uintptr_t)q & 15) == 0 &&
                      ((uintptr_t)k & 15) == 0 && (form == 1 || ((uintptr_t)pre & 15) == 0);
     const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (form == 0 ? RC * Dk : 2 * RC) + RC * JB);
-    static size_t allowed[2] = {48 << 10, 48 << 10};
     if (form != 0 && form != 1) return CW_ERR_UNSUPPORTED;
-    if (smem > allowed[form]) {
-        const cudaError_t e = form == 0 ? cudaFuncSetAttribute(recurrence_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                        : cudaFuncSetAttribute(recurrence_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool vec = wide && Dk == IP * RS;
+    const int which = form * 2 + (vec ? 1 : 0);
+    static size_t allowed[4] = {48 << 10, 48 << 10, 48 << 10, 48 << 10};
+    using Kernel = void (*)(const float*, int, const float*, int, const float*, int, const float*, int, const float*, const float*,
+                            const float*, float*, long long, long long, const long long*, const int*, const int*, int, int, int, int, int,
+                            float*, int);
+    const Kernel kernels[4] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
+                               recurrence_scan_kernel<1, true>};
+    if (smem > allowed[which]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        allowed[form] = smem;
+        allowed[which] = smem;
     }
-    if (form == 0)
-        return cw_launch(recurrence_scan_kernel<0>, grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                         state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, out, ldo);
-    return cw_launch(recurrence_scan_kernel<1>, grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+    return cw_launch(kernels[which], grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
                      state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, out, ldo);
 }
 
