@@ -84,7 +84,7 @@ extern "C" int cw_latent_prepare(const float* down, const void* q, void* qa, voi
 // the weighted sum.  The chunking depends on the token's position only, never on the rest of the batch.
 #define LA_CH 128
 #define LA_HB 4
-#define LA_NC 4  // latent columns per thread: rank <= LA_CH * LA_NC
+#define LA_NC 8  // latent columns per thread: rank <= LA_CH * LA_NC
 
 // max or sum of LA_HB values per thread over the block, in a fixed order
 template <bool MAX>
