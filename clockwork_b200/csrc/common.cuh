@@ -205,3 +205,22 @@ static inline int cw_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     if (err != cudaSuccess) return (int)err;
     return (int)cudaGetLastError();
 }
+
+// A launch in plain stream order: the kernel starts when everything before it on the stream has finished,
+// and (as it never releases its dependents early) what follows starts when it has finished.  For kernels
+// with large grids or much shared memory per block, which should not sit on the SMs waiting for a
+// predecessor while later kernels pile up behind them.
+template <typename... KArgs, typename... Args>
+static inline int cw_launch_ordered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaGetLastError();
+}

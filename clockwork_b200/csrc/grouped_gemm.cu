@@ -33,7 +33,6 @@ grouped_gemm_kernel(const T* __restrict__ A, int lda, int a_group_off, const T* 
     __shared__ float Bs[GG_TK][GG_TN + 1];
     __shared__ float B2s[EPI == GG_EPI_SILU_MUL ? GG_TK : 1][GG_TN + 1];
     __shared__ int src_s[GG_TM], dst_s[GG_TM];
-    pdl_launch_dependents();
     pdl_wait();
     // which group and which tile of its rows
     int g, row0, rows_end;
@@ -163,7 +162,6 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ A, int lda, int a_group_off, co
     bf16* Bs = As + GM_STAGES * GM_TM * GM_LD;       // [stages][TN][LD]
     bf16* B2s = Bs + GM_STAGES * GM_TN * GM_LD;      // [stages][TN][LD] (two-product form only)
     __shared__ int src_s[GM_TM], dst_s[GM_TM];
-    pdl_launch_dependents();
     pdl_wait();
     int g, row0, rows_end;
     if (offsets == nullptr) {
@@ -302,7 +300,7 @@ static int launch_grouped_mma(dim3 grid, cudaStream_t stream, const void* A, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return cw_launch(grouped_gemm_mma_kernel<EPI>, grid, dim3(256), smem, stream, 1, (const bf16*)A, lda, a_group_off, (const bf16*)B,
+    return cw_launch_ordered(grouped_gemm_mma_kernel<EPI>, grid, dim3(256), smem, stream, (const bf16*)A, lda, a_group_off, (const bf16*)B,
                      (const bf16*)B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, c_index, (const bf16*)gate, ldg, M, Nout,
                      K, G);
 }
@@ -316,7 +314,7 @@ static int launch_grouped(int epi, dim3 grid, cudaStream_t stream, const void* A
                           const int* a_index, int a_div, const int* c_index, const void* gate, int ldg, int M, int Nout, int K,
                           int G) {
 #define GG_GO(E)                                                                                                              \
-    return cw_launch(grouped_gemm_kernel<T, E>, grid, dim3(256), 0, stream, 1, (const T*)A, lda, a_group_off, (const T*)B,    \
+    return cw_launch_ordered(grouped_gemm_kernel<T, E>, grid, dim3(256), 0, stream, (const T*)A, lda, a_group_off, (const T*)B,    \
                      (const T*)B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, c_index, (const T*)gate, ldg, M,   \
                      Nout, K, G)
     switch (epi) {
@@ -377,7 +375,6 @@ __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b, const int* __restrict__ tok_seq,
                   int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top) {
     extern __shared__ float choose_s[];  // per warp: [E] logits, then [top] chosen logits
-    pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * 4 + warp;
@@ -425,7 +422,7 @@ extern "C" int cw_moe_choose(const float* logits, const float* b, const int* tok
     if (N < 0 || E <= 0 || top <= 0 || top > E) return CW_ERR_BAD_SIZE;
     const size_t smem = 4 * (size_t)(E + top) * sizeof(float);
     if (smem > (48 << 10)) return CW_ERR_UNSUPPORTED;
-    return cw_launch(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, 1, logits, b, tok_seq, sel, wt, N, E, top);
+    return cw_launch_ordered(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, logits, b, tok_seq, sel, wt, N, E, top);
 }
 
 // ---- pairs by expert --------------------------------------------------------------------------------
@@ -436,7 +433,6 @@ __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int* __restrict__ sel, int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ rank,
                  int P, int E) {
     extern __shared__ int count_s[];  // [E + 1]
-    pdl_launch_dependents();
     pdl_wait();
     for (int e = threadIdx.x; e <= E; e += blockDim.x) count_s[e] = 0;
     __syncthreads();
@@ -464,14 +460,13 @@ moe_group_kernel(const int* __restrict__ sel, int* __restrict__ offsets, int* __
 
 extern "C" int cw_moe_group(const int* sel, int* offsets, int* order, int* rank, int P, int E, cudaStream_t stream) {
     if (P < 0 || E <= 0 || E > 8191) return CW_ERR_BAD_SIZE;
-    return cw_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, 1, sel, offsets, order, rank, P, E);
+    return cw_launch_ordered(moe_group_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, sel, offsets, order, rank, P, E);
 }
 
 // resid[n] += sum_t wt[n, t] * y[n * top + t] over the choices in order.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ resid, const float* __restrict__ y, const int* __restrict__ sel,
                    const float* __restrict__ wt, int W, int top) {
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
     if (sel[(size_t)row * top] < 0) return;
@@ -486,7 +481,7 @@ extern "C" int cw_moe_combine(float* resid, const float* y, const int* sel, cons
                               cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || W <= 0 || top <= 0) return CW_ERR_BAD_SIZE;
-    return cw_launch(moe_combine_kernel, dim3(N), dim3(256), 0, stream, 1, resid, y, sel, wt, W, top);
+    return cw_launch_ordered(moe_combine_kernel, dim3(N), dim3(256), 0, stream, resid, y, sel, wt, W, top);
 }
 
 CW_TRACE_TU(grouped_gemm)

@@ -26,7 +26,6 @@ latent_prepare_kernel(const float* __restrict__ down, const T* __restrict__ q, T
                       const int* __restrict__ positions, const int* __restrict__ slots, int H, int dim, int rot, int rank,
                       int num_slots, float eps, int write_cache, int* status) {
     __shared__ float scratch[33];
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const int D = rank + rot, half = rot / 2;
@@ -71,10 +70,10 @@ extern "C" int cw_latent_prepare(const float* down, const void* q, void* qa, voi
     if (N == 0) return CW_OK;
     if (N < 0 || H <= 0 || dim < 0 || rot < 0 || rot % 2 || rank <= 0) return CW_ERR_BAD_SIZE;
     if (dtype == 0)
-        return cw_launch(latent_prepare_kernel<float>, dim3(N), dim3(128), 0, stream, 1, down, (const float*)q, (float*)qa,
+        return cw_launch_ordered(latent_prepare_kernel<float>, dim3(N), dim3(128), 0, stream, down, (const float*)q, (float*)qa,
                          (float*)cache, norm_w, inv_freq, positions, slots, H, dim, rot, rank, num_slots, eps, write_cache, status);
     if (dtype == 1)
-        return cw_launch(latent_prepare_kernel<bf16>, dim3(N), dim3(128), 0, stream, 1, down, (const bf16*)q, (bf16*)qa,
+        return cw_launch_ordered(latent_prepare_kernel<bf16>, dim3(N), dim3(128), 0, stream, down, (const bf16*)q, (bf16*)qa,
                          (bf16*)cache, norm_w, inv_freq, positions, slots, H, dim, rot, rank, num_slots, eps, write_cache, status);
     return CW_ERR_BAD_DTYPE;
 }
@@ -114,7 +113,6 @@ latent_attention_kernel(const T* __restrict__ qa, TO* __restrict__ out, const T*
     __shared__ float p_s[LA_HB][LA_CH];
     __shared__ int slot_s[LA_CH];
     __shared__ float red_s[LA_CH / 32][LA_HB];
-    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h0 = blockIdx.y * LA_HB, tid = threadIdx.x;
     const int D = rank + rot;
@@ -264,7 +262,6 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, bf16* __restrict__ out,
     float* row_max = (float*)(Plo + 16 * LT_PLD);  // [4][16]
     float* row_sum = row_max + 64;                  // [4][16]
     int* slot_s = (int*)(row_sum + 64);             // [LT_KEYS]
-    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h0 = blockIdx.y * 16, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int heads = min(16, H - h0);
@@ -445,7 +442,7 @@ extern "C" int cw_latent_attention(const void* qa, void* out, const void* cache,
     const size_t smem = (size_t)LA_HB * (rank + rot) * sizeof(float);
     dim3 grid(N, (H + LA_HB - 1) / LA_HB);
     if (dtype == 0)
-        return cw_launch(latent_attention_kernel<float, float>, grid, dim3(LA_CH), smem, stream, 1, (const float*)qa, (float*)out,
+        return cw_launch_ordered(latent_attention_kernel<float, float>, grid, dim3(LA_CH), smem, stream, (const float*)qa, (float*)out,
                          (const float*)cache, block_tables, tok_seq, positions, sink, H, rank, rot, page_size, max_blocks,
                          num_pages, scale, status);
     const int D = rank + rot;
@@ -459,12 +456,12 @@ extern "C" int cw_latent_attention(const void* qa, void* out, const void* cache,
             if (e != cudaSuccess) return (int)e;
             allowed = bytes;
         }
-        return cw_launch(latent_attention_mma_kernel, dim3(N, (H + 15) / 16), dim3(128), bytes, stream, 1, (const bf16*)qa, (bf16*)out,
+        return cw_launch_ordered(latent_attention_mma_kernel, dim3(N, (H + 15) / 16), dim3(128), bytes, stream, (const bf16*)qa, (bf16*)out,
                          (const bf16*)cache, block_tables, tok_seq, positions, sink, H, rank, rot, page_size, max_blocks, num_pages,
                          scale, status);
     }
     if (dtype == 1)
-        return cw_launch(latent_attention_kernel<bf16, bf16>, grid, dim3(LA_CH), smem, stream, 1, (const bf16*)qa, (bf16*)out,
+        return cw_launch_ordered(latent_attention_kernel<bf16, bf16>, grid, dim3(LA_CH), smem, stream, (const bf16*)qa, (bf16*)out,
                          (const bf16*)cache, block_tables, tok_seq, positions, sink, H, rank, rot, page_size, max_blocks,
                          num_pages, scale, status);
     return CW_ERR_BAD_DTYPE;

@@ -27,7 +27,6 @@ shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const fl
                  long long state_stride, long long state_off, const long long* __restrict__ slots,
                  const int* __restrict__ tok_seq, const int* __restrict__ q_start, T* __restrict__ out,
                  int N, int W, int mixes) {
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
     const int seq = tok_seq[row];
@@ -54,10 +53,10 @@ extern "C" int cw_shift_mix(const void* x, const float* mu, const float* state, 
     if (N == 0) return CW_OK;
     if (N < 0 || W <= 0 || mixes <= 0) return CW_ERR_BAD_SIZE;
     if (dtype == 0)
-        return cw_launch(shift_mix_kernel<float>, dim3(N), dim3(256), 0, stream, 1, (const float*)x, mu, state, state_stride,
+        return cw_launch_ordered(shift_mix_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)x, mu, state, state_stride,
                          state_off, slots, tok_seq, q_start, (float*)out, N, W, mixes);
     if (dtype == 1)
-        return cw_launch(shift_mix_kernel<bf16>, dim3(N), dim3(256), 0, stream, 1, (const bf16*)x, mu, state, state_stride,
+        return cw_launch_ordered(shift_mix_kernel<bf16>, dim3(N), dim3(256), 0, stream, (const bf16*)x, mu, state, state_stride,
                          state_off, slots, tok_seq, q_start, (bf16*)out, N, W, mixes);
     return CW_ERR_BAD_DTYPE;
 }
@@ -70,7 +69,6 @@ causal_conv_kernel(const float* __restrict__ x, int ldx, const float* __restrict
                    const float* __restrict__ state, long long state_stride, long long state_off,
                    const long long* __restrict__ slots, const int* __restrict__ tok_seq, const int* __restrict__ q_start,
                    float* __restrict__ out, int C, int taps) {
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
     const int seq = tok_seq[row];
@@ -97,7 +95,7 @@ extern "C" int cw_causal_conv(const float* x, int ldx, const float* weight, cons
                               const int* q_start, float* out, int N, int C, int taps, cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || C <= 0 || taps <= 0 || ldx < C) return CW_ERR_BAD_SIZE;
-    return cw_launch(causal_conv_kernel, dim3(N), dim3(256), 0, stream, 1, x, ldx, weight, bias, state, state_stride, state_off,
+    return cw_launch_ordered(causal_conv_kernel, dim3(N), dim3(256), 0, stream, x, ldx, weight, bias, state, state_stride, state_off,
                      slots, tok_seq, q_start, out, C, taps);
 }
 
@@ -109,7 +107,6 @@ __global__ void __launch_bounds__(256)
 carry_rows_kernel(const T* __restrict__ x, int ldx, float* __restrict__ state, long long state_stride,
                   long long state_off, const long long* __restrict__ slots, const int* __restrict__ tok_seq,
                   const int* __restrict__ q_start, int C, int R) {
-    pdl_launch_dependents();
     pdl_wait();
     const int seq = blockIdx.x;
     const int start = q_start[seq], end = q_start[seq + 1];
@@ -129,10 +126,10 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
     if (S < 0 || C <= 0 || R < 0 || ldx < C) return CW_ERR_BAD_SIZE;
     dim3 grid(S, min(64, (C + 255) / 256));
     if (dtype == 0)
-        return cw_launch(carry_rows_kernel<float>, grid, dim3(256), 0, stream, 1, (const float*)x, ldx, state, state_stride,
+        return cw_launch_ordered(carry_rows_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ldx, state, state_stride,
                          state_off, slots, tok_seq, q_start, C, R);
     if (dtype == 1)
-        return cw_launch(carry_rows_kernel<bf16>, grid, dim3(256), 0, stream, 1, (const bf16*)x, ldx, state, state_stride,
+        return cw_launch_ordered(carry_rows_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, state, state_stride,
                          state_off, slots, tok_seq, q_start, C, R);
     return CW_ERR_BAD_DTYPE;
 }
@@ -141,10 +138,42 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
 // Per request and head a state S [Dk, Dv] (float32, stored value-column-major: element (i, j) of head h at
 // (h*Dv + j)*Dk + i).  Two forms:
 //   FORM 0 (decay per key channel, output before the update, bonus for the current token):
-//       a_i = exp(-exp(pre_i + p0_i));  y_j = sum_i q_i (S_ij + p1_i k_i v_j);  S_ij <- a_i S_ij + k_i v_j
+//       y_j = sum_i q_i (S_ij + p1_i k_i v_j);  S_ij <- a_i S_ij + k_i v_j          (coef = a [N, H*Dk])
 //   FORM 1 (one decay per head from a step size, output after the update, skip term):
-//       dt = softplus(pre + p0);  a = exp(-exp(p1) dt);  S_ij <- a S_ij + dt k_i v_j;  y_j = sum_i q_i S_ij + p2 v_j
+//       S_ij <- a S_ij + dt k_i v_j;  y_j = sum_i q_i S_ij + p2 v_j                  (coef = [a | dt] [N, 2H])
+// with the coefficients from cw_recurrence_coefficients.
 // q and k of head h are those of group h / heads_per_group.  Blocks: (request, head, slice of value columns).
+// What the recurrence multiplies by, computed once per token before the scan (float32):
+//   FORM 0: a[t, c] = exp(-exp(pre[t, c] + p0[c])) for the H*Dk channels, in place
+//   FORM 1: dt = softplus(pre[t, h] + p0[h]) (no threshold), out[t, h] = exp(-exp(p1[h]) dt), out[t, H + h] = dt
+__global__ void __launch_bounds__(256)
+recurrence_coefficients_kernel(int form, float* __restrict__ pre, int ldp, const float* __restrict__ p0,
+                               const float* __restrict__ p1, float* __restrict__ out, int N, int C) {
+    pdl_wait();
+    const long long total = (long long)N * C;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / C), c = (int)(idx - (long long)t * C);
+        if (form == 0) {
+            float* at = pre + (size_t)t * ldp + c;
+            *at = expf(-expf(*at + p0[c]));
+        } else {
+            const float x = pre[(size_t)t * ldp + c] + p0[c];
+            const float dt = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
+            out[(size_t)t * 2 * C + c] = expf(-expf(p1[c]) * dt);
+            out[(size_t)t * 2 * C + C + c] = dt;
+        }
+    }
+}
+
+extern "C" int cw_recurrence_coefficients(int form, float* pre, int ldp, const float* p0, const float* p1, float* out, int N, int C,
+                                          cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || C <= 0 || ldp < C || (form != 0 && form != 1)) return CW_ERR_BAD_SIZE;
+    const long long total = (long long)N * C;
+    const int blocks = (int)min((long long)148 * 8, (total + 255) / 256);
+    return cw_launch_ordered(recurrence_coefficients_kernel, dim3(blocks), dim3(256), 0, stream, form, pre, ldp, p0, p1, out, N, C);
+}
+
 #define RS 8    // key channels per thread
 #define RC 16   // tokens per staged chunk
 
@@ -158,8 +187,7 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 }
 
 // The operands of RC tokens at a time are copied into shared memory (cp.async, the next chunk while the
-// current one is computed), turned into what the recurrence multiplies by (decays, step-scaled keys) once
-// per block, and read from there by the IP x JB threads; a thread owns key channels ipart, ipart + IP, ..
+// current one is computed) and read from there by the IP x JB threads; a thread owns key channels ipart, ipart + IP, ..
 // of value column j, so that neighbouring lanes read neighbouring words of shared memory and of the state.
 // The per-token sums over key channels are reduced over the IP lanes of a column after the chunk's loop.
 template <int FORM, bool VEC>
@@ -169,10 +197,9 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                        const float* __restrict__ p0, const float* __restrict__ p1, const float* __restrict__ p2,
                        float* __restrict__ state, long long state_stride, long long state_off,
                        const long long* __restrict__ slots, const int* __restrict__ tok_seq,
-                       const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP, int wide,
+                       const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP, int wide, int H,
                        float* __restrict__ out, int ldo) {
     extern __shared__ __align__(16) float rs_smem[];
-    pdl_launch_dependents();
     pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int start = q_start[seq], end = q_start[seq + 1];
@@ -201,12 +228,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         S[r] = (on && live) ? S_mem[i] : 0.f;
         if (FORM == 0) c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
     }
-    float head_p0 = 0.f, head_decay = 0.f, head_skip = 0.f;
-    if (FORM == 1) {
-        head_p0 = p0[h];
-        head_decay = expf(p1[h]);
-        head_skip = p2 != nullptr ? p2[h] : 0.f;
-    }
+    const float head_skip = (FORM == 1 && p2 != nullptr) ? p2[h] : 0.f;
     const float* qp = q + (size_t)g * Dk;
     const float* kp = k + (size_t)g * Dk;
     const float* pp = FORM == 0 ? pre + (size_t)h * Dk : pre + h;
@@ -220,8 +242,9 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         float* vs = as + a_words;
         if (wide) {  // rows of whole 16-byte pieces at 16-byte addresses
             const int pieces = Dk >> 2;
+            const int shift = VEC ? 31 - __clz(pieces) : 0;  // (VEC: Dk = 8 * 2^n, so a power of two)
             for (int idx = tid; idx < n * pieces; idx += blockDim.x) {
-                const int t = idx / pieces, i = (idx - t * pieces) << 2;
+                const int t = VEC ? idx >> shift : idx / pieces, i = (idx - t * pieces) << 2;
                 cp_async16f(qs + t * Dk + i, qp + (size_t)(t0 + t) * ldq + i);
                 cp_async16f(ks + t * Dk + i, kp + (size_t)(t0 + t) * ldk + i);
                 if (FORM == 0) cp_async16f(as + t * Dk + i, pp + (size_t)(t0 + t) * ldp + i);
@@ -235,7 +258,10 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
             }
         }
         if (FORM == 1)
-            for (int t = tid; t < n; t += blockDim.x) cp_async4(as + t, pp + (size_t)(t0 + t) * ldp);
+            for (int t = tid; t < 2 * n; t += blockDim.x) {  // a and dt of the head
+                const int tok = t >> 1, second = t & 1;
+                cp_async4(as + second * RC + tok, pp + (size_t)(t0 + tok) * ldp + second * H);
+            }
         for (int idx = tid; idx < n * nv; idx += blockDim.x) {
             const int t = idx / nv, c = idx - t * nv;
             cp_async4(vs + t * JB + c, vp + (size_t)(t0 + t) * ldv + c);
@@ -254,29 +280,14 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();  // this chunk has landed; everyone has left the other buffer
         if (t0 + RC < end) fetch(t0 + RC, rs_smem + (which ^ 1) * buf_words);
-        if (FORM == 0) {
-            for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
-                const int i = idx % Dk;
-                as[idx] = expf(-expf(as[idx] + p0[(size_t)h * Dk + i]));
-            }
-        } else {
-            if (tid < n) {
-                const float x = as[tid] + head_p0;
-                const float dt = fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));  // softplus without a threshold
-                as[RC + tid] = dt;
-                as[tid] = expf(-head_decay * dt);
-            }
-            __syncthreads();
-            for (int idx = tid; idx < n * Dk; idx += blockDim.x) ks[idx] *= as[RC + idx / Dk];
-        }
-        __syncthreads();
         float part[RC];
 #pragma unroll
         for (int t = 0; t < RC; ++t) {
             part[t] = 0.f;
             if (t < n) {
-                const float vc = live ? vs[t * JB + jl] : 0.f;
+                const float vraw = live ? vs[t * JB + jl] : 0.f;
                 const float a1 = FORM == 1 ? as[t] : 0.f;
+                const float vc = FORM == 1 ? vraw * as[RC + t] : vraw;  // the step size scales the update
                 float sum = 0.f;
                 if (VEC) {
                     const int at = t * Dk + i_first;
@@ -340,6 +351,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     }
 }
 
+// pre: the coefficients that cw_recurrence_coefficients made (form 0: a [N, H*Dk]; form 1: [a | dt] [N, 2H]).
 extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                                   const float* pre, int ldp, const float* p0, const float* p1, const float* p2,
                                   float* state, long long state_stride, long long state_off, const long long* slots,
@@ -362,7 +374,7 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     const int which = form * 2 + (vec ? 1 : 0);
     static size_t allowed[4] = {48 << 10, 48 << 10, 48 << 10, 48 << 10};
     using Kernel = void (*)(const float*, int, const float*, int, const float*, int, const float*, int, const float*, const float*,
-                            const float*, float*, long long, long long, const long long*, const int*, const int*, int, int, int, int, int,
+                            const float*, float*, long long, long long, const long long*, const int*, const int*, int, int, int, int, int, int,
                             float*, int);
     const Kernel kernels[4] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
                                recurrence_scan_kernel<1, true>};
@@ -371,8 +383,8 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
         if (e != cudaSuccess) return (int)e;
         allowed[which] = smem;
     }
-    return cw_launch(kernels[which], grid, dim3(threads), smem, stream, 1, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, out, ldo);
+    return cw_launch_ordered(kernels[which], grid, dim3(threads), smem, stream, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
+                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, H, out, ldo);
 }
 
 // ---- gated norm in parts ----------------------------------------------------------------------------
@@ -383,7 +395,6 @@ __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ weight,
                         T* __restrict__ out, int C, int parts, float eps, int gate_first) {
     __shared__ float scratch[33];
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, p = blockIdx.y;
     const int width = C / parts;
@@ -419,10 +430,10 @@ extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, cons
     while (threads < 256 && threads * 4 < width) threads *= 2;
     dim3 grid(N, parts);
     if (dtype == 0)
-        return cw_launch(gated_group_norm_kernel<float>, grid, dim3(threads), 0, stream, 1, y, z, ldz, weight, (float*)out, C, parts,
+        return cw_launch_ordered(gated_group_norm_kernel<float>, grid, dim3(threads), 0, stream, y, z, ldz, weight, (float*)out, C, parts,
                          eps, gate_first);
     if (dtype == 1)
-        return cw_launch(gated_group_norm_kernel<bf16>, grid, dim3(threads), 0, stream, 1, y, z, ldz, weight, (bf16*)out, C, parts,
+        return cw_launch_ordered(gated_group_norm_kernel<bf16>, grid, dim3(threads), 0, stream, y, z, ldz, weight, (bf16*)out, C, parts,
                          eps, gate_first);
     return CW_ERR_BAD_DTYPE;
 }
@@ -430,7 +441,6 @@ extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, cons
 // ---- activations in place -----------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) activation_kernel(T* __restrict__ x, long long n, int kind) {
-    pdl_launch_dependents();
     pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const float z = to_f(x[i]);
@@ -447,8 +457,8 @@ extern "C" int cw_activation(void* x, long long n, int kind, int dtype, cudaStre
     if (n == 0) return CW_OK;
     if (n < 0 || kind < 0 || kind > 1) return CW_ERR_BAD_SIZE;
     const int blocks = (int)min((long long)148 * 8, (n + 255) / 256);
-    if (dtype == 0) return cw_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (float*)x, n, kind);
-    if (dtype == 1) return cw_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (bf16*)x, n, kind);
+    if (dtype == 0) return cw_launch_ordered(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n, kind);
+    if (dtype == 1) return cw_launch_ordered(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, n, kind);
     return CW_ERR_BAD_DTYPE;
 }
 

@@ -35,6 +35,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_causal_conv": [P, I, P, P, P, LL, LL, P, P, P, P, I, I, I, P],
     "cw_carry_rows": [P, I, P, LL, LL, P, P, P, I, I, I, I, P],
     "cw_recurrence_scan": [I, P, I, P, I, P, I, P, I, P, P, P, P, LL, LL, P, P, P, I, I, I, I, I, P, I, P],
+    "cw_recurrence_coefficients": [I, P, I, P, P, P, I, I, P],
     "cw_gated_group_norm": [P, P, I, P, P, I, I, I, F, I, I, P],
     "cw_activation": [P, LL, I, I, P],
     # products in groups and the mixture of experts (csrc/grouped_gemm.cu)

@@ -68,7 +68,8 @@ def recurrence_scan(form: int, q, k, v, pre, p0, p1, p2, view, offset: int, ctx,
                     heads_per_group: int = 1) -> torch.Tensor:
     """float32 [N, heads*dv].  ``q``, ``k`` [N, groups*dk], ``v`` [N, heads*dv], ``pre`` [N, heads*dk] (form 0) or
     [N, heads] (form 1): float32, unit column stride, any row stride.  The state piece at ``offset`` holds
-    heads*dk*dv numbers."""
+    heads*dk*dv numbers.  Form 0 turns ``pre`` into the decays in place (it is a product's output that nothing
+    else reads)."""
     for name, t in (("q", q), ("k", k), ("v", v), ("pre", pre)):
         if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise ValueError(f"{name} must be float32 [N, *] with unit column stride")
@@ -79,6 +80,15 @@ def recurrence_scan(form: int, q, k, v, pre, p0, p1, p2, view, offset: int, ctx,
     def ld(t):
         return t.stride(0) if n > 1 else max(t.stride(0), t.shape[1])
 
+    # decays and step sizes once per token, ahead of the scan
+    if form == FORM_CHANNEL_DECAY:
+        check(library().cw_recurrence_coefficients(form, _ptr(pre), ld(pre), _ptr(p0), None, None, n, heads * dk, _stream()),
+              "recurrence_coefficients")
+    else:
+        coef = torch.empty((n, 2 * heads), dtype=torch.float32, device=v.device)
+        check(library().cw_recurrence_coefficients(form, _ptr(pre), ld(pre), _ptr(p0), _ptr(p1), _ptr(coef), n, heads, _stream()),
+              "recurrence_coefficients")
+        pre = coef
     check(library().cw_recurrence_scan(form, _ptr(q), ld(q), _ptr(k), ld(k), _ptr(v), ld(v), _ptr(pre), ld(pre), _ptr(p0), _ptr(p1),
                                        _ptr(p2), state, stride, offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs,
                                        heads, dk, dv, heads_per_group, _ptr(out), heads * dv, _stream()), "recurrence_scan")
