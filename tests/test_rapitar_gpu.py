@@ -403,3 +403,39 @@ def test_products_in_groups_on_tensor_cores(experts, top, ff, w, n):
     for got in outs:
         assert float((got.double() - want).abs().max()) <= 3 * yard
     assert float((outs[0] - outs[1]).abs().max()) <= yard
+
+
+@pytest.mark.timeout(600)
+def test_a_step_of_eight_layers_at_layer_sizes_of_published_models():
+    """Eight layers at 2,048 width (grids of thousands of blocks, blocks with tens of kilobytes of shared memory, some
+    300 launches a step): prompt portions and single-token steps through the captured graphs finish and agree with the
+    same steps launched kernel by kernel."""
+    from clockwork_b200.cache import CacheManager
+    from clockwork_b200.cli import shape_config
+    from clockwork_b200.engine import ModelRunner, StepEntry, random_model
+
+    raw = shape_config("rapitar-2k")
+    model = random_model(raw, seed=3, dtype="bfloat16", device=DEV)
+    prompt = tokens_for({"vocab": raw["vocab"]}, 300, salt=9)
+    tail = tokens_for({"vocab": raw["vocab"]}, 3, salt=10)
+    results = []
+    for graphs in (True, False):
+        cache = CacheManager(model.cache_needs(), num_pages=64, page_size=16, dtype=model.dtype, device=DEV, num_state_slots=2)
+        runner = ModelRunner(model, cache)
+        if graphs:
+            assert runner.enable_graphs(max_ctx=1024, max_batch=2)
+        cache.open("a")
+        rows = [runner.step([StepEntry("a", prompt, [len(prompt) - 1])]).float().cpu()]
+        for t in tail:
+            entry = [StepEntry("a", [t], [0])]
+            if graphs:
+                runner.decode_with_graph(entry, None)
+                rows.append(runner.last_graph.logits[:1].float().cpu())
+            else:
+                rows.append(runner.step(entry).float().cpu())
+        runner.check_status()
+        assert not graphs or (runner.portion_graph_steps == 1 and runner.graphs)
+        results.append(torch.cat(rows))
+    assert torch.isfinite(results[0]).all()
+    scale = float(results[1].abs().max())
+    assert float((results[0] - results[1]).abs().max()) <= 0.02 * scale
