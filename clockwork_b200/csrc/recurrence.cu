@@ -217,13 +217,15 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     const int buf_words = 2 * RC * Dk + a_words + RC * JB;
     const int g = h / heads_per_group;
     float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
-    // VEC (Dk == 8 IP): a thread owns the eight consecutive channels 8 ipart .., read as two 16-byte words per
-    // operand and token; otherwise channels ipart, ipart + IP, .. one word at a time
-    const int i_first = VEC ? ipart * RS : ipart, i_step = VEC ? 1 : IP;
+    // VEC (Dk == 8 IP): a thread owns channels 4 ipart .. 4 ipart + 3 and the same four in the upper half, read as
+    // two 16-byte words per operand and token (neighbouring lanes read neighbouring words: no bank conflicts);
+    // otherwise channels ipart, ipart + IP, .. one word at a time
+    const int half = Dk >> 1;
+    auto channel = [&](int r) { return VEC ? (r < 4 ? 0 : half) + ipart * 4 + (r & 3) : ipart + r * IP; };
     float S[RS], c1[RS];
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
-        const int i = i_first + r * i_step;
+        const int i = channel(r);
         const bool on = i < Dk;
         S[r] = (on && live) ? S_mem[i] : 0.f;
         if (FORM == 0) c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
@@ -290,15 +292,15 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                 const float vc = FORM == 1 ? vraw * as[RC + t] : vraw;  // the step size scales the update
                 float sum = 0.f;
                 if (VEC) {
-                    const int at = t * Dk + i_first;
+                    const int at = t * Dk + ipart * 4, up = at + half;
                     float kc[RS], qc[RS], ac[RS];
                     *(float4*)&kc[0] = *(const float4*)(ks + at);
-                    *(float4*)&kc[4] = *(const float4*)(ks + at + 4);
+                    *(float4*)&kc[4] = *(const float4*)(ks + up);
                     *(float4*)&qc[0] = *(const float4*)(qs + at);
-                    *(float4*)&qc[4] = *(const float4*)(qs + at + 4);
+                    *(float4*)&qc[4] = *(const float4*)(qs + up);
                     if (FORM == 0) {
                         *(float4*)&ac[0] = *(const float4*)(as + at);
-                        *(float4*)&ac[4] = *(const float4*)(as + at + 4);
+                        *(float4*)&ac[4] = *(const float4*)(as + up);
                     }
                     float sum2 = 0.f;  // two chains of four, added at the end: the same order for every token and batch
 #pragma unroll
@@ -345,7 +347,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     if (live) {
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
-            const int i = i_first + r * i_step;
+            const int i = channel(r);
             if (i < Dk) S_mem[i] = S[r];
         }
     }
