@@ -139,14 +139,20 @@ class CacheManager:
         self.device = torch.device(device) if device is not None else None
         by_need: dict[PagedKVNeed, list[int]] = {}
         state_needs: dict[int, SlotStateNeed] = {}
+        self.view_order: dict[int, tuple] = {}  # layers whose mixer keeps several things: the kinds, in its order
         for layer in sorted(needs):
-            need = needs[layer]
-            if isinstance(need, PagedKVNeed):
-                by_need.setdefault(need, []).append(layer)
-            elif isinstance(need, SlotStateNeed):
-                state_needs[layer] = need
-            else:
-                raise TypeError(f"cache layer {layer}: unknown need {need!r}")
+            several = isinstance(needs[layer], tuple)
+            kinds = []
+            for need in (needs[layer] if several else (needs[layer],)):
+                if isinstance(need, PagedKVNeed) and PagedKVNeed not in kinds:
+                    by_need.setdefault(need, []).append(layer)
+                elif isinstance(need, SlotStateNeed) and SlotStateNeed not in kinds:
+                    state_needs[layer] = need
+                else:
+                    raise TypeError(f"cache layer {layer}: unknown need {need!r} (or two of a kind in one layer)")
+                kinds.append(type(need))
+            if several:
+                self.view_order[layer] = tuple(kinds)
         self.groups = [PageGroup(need, layers, num_pages, page_size, dtype, device) for need, layers in by_need.items()]
         self.group_of_layer = {layer: g for g, group in enumerate(self.groups) for layer in group.cache_layers}
         self.state = StateSlots(state_needs, num_state_slots, device)
@@ -343,7 +349,15 @@ class CacheManager:
                 k, v = group.layer_kv(layer)
                 out[layer] = PagedView(k, v, block_tables[g], slots[g], True)
         for layer, tensor in self.state.tensors.items():
-            out[layer] = StateView(tensor, state_slots, list(state_slots_host))
+            view = StateView(tensor, state_slots, list(state_slots_host))
+            if layer in self.view_order:  # the mixer keeps pages as well: both views, in the order it named its needs
+                both = {PagedKVNeed: out.get(layer), SlotStateNeed: view}
+                out[layer] = tuple(both[kind] for kind in self.view_order[layer])
+            else:
+                out[layer] = view
+        for layer, kinds in self.view_order.items():
+            if not isinstance(out[layer], tuple):  # (a tuple of one need)
+                out[layer] = (out[layer],)
         return out
 
     # ---- accounting -----------------------------------------------------------------------------

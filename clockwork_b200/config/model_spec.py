@@ -73,6 +73,8 @@ class ModelSpec:
     tie_word_embeddings: bool = False
     eos_token_ids: tuple[int, ...] = ()
     max_position_embeddings: int | None = None
+    embedding_scale: float = 1.0  # the embedding rows are multiplied by this (the output head, if tied, is not)
+    absolute_positions: PartSpec | None = None  # a position part that adds a vector per position to the embedding
     raw: dict[str, Any] = field(default_factory=dict)  # the config.json it came from
 
     def validate(self) -> None:

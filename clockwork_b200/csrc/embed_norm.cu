@@ -312,6 +312,57 @@ extern "C" int cw_add_to_residual(float* resid, const void* delta, int N, int H,
     return CW_LAUNCH_CHECK();
 }
 
+// ---- an embedding's scale and absolute positions ------------------------------------------------------
+// x[row, c] <- x[row, c] * scale + (c even ? sin : cos)(position[row] * inv_freq[c / 2]): the sinusoidal
+// position vector of width W added to the (scaled) embedding rows.  Angles in float32.
+__global__ void __launch_bounds__(256)
+scale_add_sinusoid_kernel(float* __restrict__ x, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                          float scale, int W) {
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float p = (float)positions[row];
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float angle = p * inv_freq[c >> 1];
+        const float pe = (c & 1) ? cosf(angle) : sinf(angle);
+        x[(size_t)row * W + c] = fmaf(x[(size_t)row * W + c], scale, pe);
+    }
+}
+
+extern "C" int cw_scale_add_sinusoid(float* x, const int* positions, const float* inv_freq, float scale, int N, int W,
+                                     cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0) return CW_ERR_BAD_SIZE;
+    return cw_launch_ordered(scale_add_sinusoid_kernel, dim3(N), dim3(256), 0, stream, x, positions, inv_freq, scale, W);
+}
+
+// ---- two contributions, each normed over the width, into the residual ---------------------------------
+// resid[row] += factor * (a[row] / rms(a[row]) * wa + b[row] / rms(b[row]) * wb), everything float32.
+__global__ void __launch_bounds__(256)
+pair_rmsnorm_add_kernel(float* __restrict__ resid, const float* __restrict__ a, const float* __restrict__ b,
+                        const float* __restrict__ wa, const float* __restrict__ wb, float eps, float factor, int W) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t at = (size_t)blockIdx.x * W;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float u = a[at + c], v = b[at + c];
+        sa = fmaf(u, u, sa);
+        sb = fmaf(v, v, sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ia = 1.0f / sqrtf(sa / (float)W + eps), ib = 1.0f / sqrtf(sb / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x)
+        resid[at + c] += factor * (a[at + c] * ia * wa[c] + b[at + c] * ib * wb[c]);
+}
+
+extern "C" int cw_pair_rmsnorm_add(float* resid, const float* a, const float* b, const float* wa, const float* wb, float eps,
+                                   float factor, int N, int W, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0) return CW_ERR_BAD_SIZE;
+    return cw_launch_ordered(pair_rmsnorm_add_kernel, dim3(N), dim3(256), 0, stream, resid, a, b, wa, wb, eps, factor, W);
+}
+
 static int g_pdl = 1;
 extern "C" int cw_pdl_enabled() { return g_pdl; }
 extern "C" int cw_set_pdl(int on) { g_pdl = on ? 1 : 0; return CW_OK; }

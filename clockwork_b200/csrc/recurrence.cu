@@ -14,7 +14,7 @@
 //                       float32 state, one pass over the portion in token order
 //   cw_gated_group_norm y (*silu(z)) divided by its root mean square in equal parts, times a weight
 //                       (times silu(z)): the gate before or after the norm
-//   cw_activation       gelu (tanh form), tanh, in place
+//   cw_activation       gelu (tanh form), tanh, silu, sigmoid, in place (cw_activation_cols: on some columns of wider rows)
 //
 // Everything that enters the recurrence (decays, step sizes, the state, the norm) is float32 in both
 // run precisions; T only names the type of activations that matrix products read or wrote.
@@ -141,7 +141,11 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
 //       y_j = sum_i q_i (S_ij + p1_i k_i v_j);  S_ij <- a_i S_ij + k_i v_j          (coef = a [N, H*Dk])
 //   FORM 1 (one decay per head from a step size, output after the update, skip term):
 //       S_ij <- a S_ij + dt k_i v_j;  y_j = sum_i q_i S_ij + p2 v_j                  (coef = [a | dt] [N, 2H])
-// with the coefficients from cw_recurrence_coefficients.
+//   FORM 2 (decay per key channel, output after the update):
+//       S_ij <- a_i S_ij + k_i v_j;  y_j = q_scale sum_i q_i S_ij                   (coef = a [N, H*Dk])
+//   FORM 3 (one constant decay per head, output after the update):
+//       S_ij <- p0_h S_ij + k_i v_j;  y_j = q_scale sum_i q_i S_ij                  (no coefficients)
+// with the coefficients from cw_recurrence_coefficients (forms 0 and 1) or cw_sigmoid_power_decay (form 2).
 // q and k of head h are those of group h / heads_per_group.  Blocks: (request, head, slice of value columns).
 // What the recurrence multiplies by, computed once per token before the scan (float32):
 //   FORM 0: a[t, c] = exp(-exp(pre[t, c] + p0[c])) for the H*Dk channels, in place
@@ -198,7 +202,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                        float* __restrict__ state, long long state_stride, long long state_off,
                        const long long* __restrict__ slots, const int* __restrict__ tok_seq,
                        const int* __restrict__ q_start, int Dk, int Dv, int heads_per_group, int IP, int wide, int H,
-                       float* __restrict__ out, int ldo) {
+                       float* __restrict__ out, int ldo, float q_scale) {
     extern __shared__ __align__(16) float rs_smem[];
     pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -212,8 +216,9 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
             for (int t = start; t < end; ++t) out[(size_t)t * ldo + (size_t)h * Dv + j] = 0.f;
         return;
     }
-    // one buffer: q [RC][Dk], k [RC][Dk], a [RC][Dk] (FORM 0) or a, dt [2][RC] (FORM 1), v [RC][JB]
-    const int a_words = FORM == 0 ? RC * Dk : 2 * RC;
+    // one buffer: q [RC][Dk], k [RC][Dk], a [RC][Dk] (forms 0 and 2) or a, dt [2][RC] (FORM 1) or nothing (FORM 3), v [RC][JB]
+    constexpr bool CH = FORM == 0 || FORM == 2;  // a decay per key channel and token
+    const int a_words = CH ? RC * Dk : (FORM == 1 ? 2 * RC : 0);
     const int buf_words = 2 * RC * Dk + a_words + RC * JB;
     const int g = h / heads_per_group;
     float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
@@ -231,9 +236,10 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         if (FORM == 0) c1[r] = on ? p1[(size_t)h * Dk + i] : 0.f;
     }
     const float head_skip = (FORM == 1 && p2 != nullptr) ? p2[h] : 0.f;
+    const float head_decay = FORM == 3 ? p0[h] : 0.f;
     const float* qp = q + (size_t)g * Dk;
     const float* kp = k + (size_t)g * Dk;
-    const float* pp = FORM == 0 ? pre + (size_t)h * Dk : pre + h;
+    const float* pp = CH ? pre + (size_t)h * Dk : (FORM == 1 ? pre + h : nullptr);
     const float* vp = v + (size_t)h * Dv + j0;
     const int nv = min(JB, Dv - j0);
     auto fetch = [&](int t0, float* buf) {  // raw operands of tokens t0 .. t0+RC-1 (those below `end`)
@@ -249,14 +255,14 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                 const int t = VEC ? idx >> shift : idx / pieces, i = (idx - t * pieces) << 2;
                 cp_async16f(qs + t * Dk + i, qp + (size_t)(t0 + t) * ldq + i);
                 cp_async16f(ks + t * Dk + i, kp + (size_t)(t0 + t) * ldk + i);
-                if (FORM == 0) cp_async16f(as + t * Dk + i, pp + (size_t)(t0 + t) * ldp + i);
+                if (CH) cp_async16f(as + t * Dk + i, pp + (size_t)(t0 + t) * ldp + i);
             }
         } else {
             for (int idx = tid; idx < n * Dk; idx += blockDim.x) {
                 const int t = idx / Dk, i = idx - t * Dk;
                 cp_async4(qs + idx, qp + (size_t)(t0 + t) * ldq + i);
                 cp_async4(ks + idx, kp + (size_t)(t0 + t) * ldk + i);
-                if (FORM == 0) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
+                if (CH) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
             }
         }
         if (FORM == 1)
@@ -288,7 +294,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
             part[t] = 0.f;
             if (t < n) {
                 const float vraw = live ? vs[t * JB + jl] : 0.f;
-                const float a1 = FORM == 1 ? as[t] : 0.f;
+                const float a1 = FORM == 1 ? as[t] : head_decay;
                 const float vc = FORM == 1 ? vraw * as[RC + t] : vraw;  // the step size scales the update
                 float sum = 0.f;
                 if (VEC) {
@@ -298,7 +304,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                     *(float4*)&kc[4] = *(const float4*)(ks + up);
                     *(float4*)&qc[0] = *(const float4*)(qs + at);
                     *(float4*)&qc[4] = *(const float4*)(qs + up);
-                    if (FORM == 0) {
+                    if (CH) {
                         *(float4*)&ac[0] = *(const float4*)(as + at);
                         *(float4*)&ac[4] = *(const float4*)(as + up);
                     }
@@ -311,7 +317,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                             acc_sum = fmaf(qc[r], fmaf(c1[r], kv, S[r]), acc_sum);
                             S[r] = fmaf(ac[r], S[r], kv);
                         } else {
-                            S[r] = fmaf(a1, S[r], kv);
+                            S[r] = fmaf(CH ? ac[r] : a1, S[r], kv);
                             acc_sum = fmaf(qc[r], S[r], acc_sum);
                         }
                     }
@@ -326,7 +332,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                                 sum = fmaf(qc, fmaf(c1[r], kv, S[r]), sum);
                                 S[r] = fmaf(as[t * Dk + i], S[r], kv);
                             } else {
-                                S[r] = fmaf(a1, S[r], kv);
+                                S[r] = fmaf(CH ? as[t * Dk + i] : a1, S[r], kv);
                                 sum = fmaf(qc, S[r], sum);
                             }
                         }
@@ -341,7 +347,9 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         if (live && ipart == 0) {
 #pragma unroll
             for (int t = 0; t < RC; ++t)
-                if (t < n) out[(size_t)(t0 + t) * ldo + (size_t)h * Dv + j] = FORM == 1 ? fmaf(head_skip, vs[t * JB + jl], part[t]) : part[t];
+                if (t < n)
+                    out[(size_t)(t0 + t) * ldo + (size_t)h * Dv + j] =
+                        FORM == 1 ? fmaf(head_skip, vs[t * JB + jl], part[t]) : (FORM >= 2 ? part[t] * q_scale : part[t]);
         }
     }
     if (live) {
@@ -358,7 +366,7 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
                                   const float* pre, int ldp, const float* p0, const float* p1, const float* p2,
                                   float* state, long long state_stride, long long state_off, const long long* slots,
                                   const int* tok_seq, const int* q_start, int S, int H, int Dk, int Dv, int heads_per_group, float* out, int ldo,
-                                  cudaStream_t stream) {
+                                  float q_scale, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || H <= 0 || Dk <= 0 || Dv <= 0 || heads_per_group <= 0 || H % heads_per_group) return CW_ERR_BAD_SIZE;
     if (Dk > 32 * RS || H > 65535) return CW_ERR_UNSUPPORTED;
@@ -368,46 +376,76 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     while (threads > 32 && threads / IP >= 2 * Dv) threads /= 2;
     const int JB = threads / IP;
     dim3 grid(S, H, (Dv + JB - 1) / JB);
-    const int wide = Dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (form == 1 || ldp % 4 == 0) && ((uintptr_t)q & 15) == 0 &&
-                     ((uintptr_t)k & 15) == 0 && (form == 1 || ((uintptr_t)pre & 15) == 0);
-    const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (form == 0 ? RC * Dk : 2 * RC) + RC * JB);
-    if (form != 0 && form != 1) return CW_ERR_UNSUPPORTED;
+    if (form < 0 || form > 3) return CW_ERR_UNSUPPORTED;
+    const bool ch = form == 0 || form == 2;  // coefficients per key channel
+    if ((form != 3 && pre == nullptr) || (form == 3 && p0 == nullptr)) return CW_ERR_BAD_SIZE;
+    const int wide = Dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (!ch || ldp % 4 == 0) && ((uintptr_t)q & 15) == 0 &&
+                     ((uintptr_t)k & 15) == 0 && (!ch || ((uintptr_t)pre & 15) == 0);
+    const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (ch ? RC * Dk : (form == 1 ? 2 * RC : 0)) + RC * JB);
     const bool vec = wide && Dk == IP * RS;
     const int which = form * 2 + (vec ? 1 : 0);
-    static size_t allowed[4] = {48 << 10, 48 << 10, 48 << 10, 48 << 10};
+    static size_t allowed[8] = {48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10};
     using Kernel = void (*)(const float*, int, const float*, int, const float*, int, const float*, int, const float*, const float*,
                             const float*, float*, long long, long long, const long long*, const int*, const int*, int, int, int, int, int, int,
-                            float*, int);
-    const Kernel kernels[4] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
-                               recurrence_scan_kernel<1, true>};
+                            float*, int, float);
+    const Kernel kernels[8] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
+                               recurrence_scan_kernel<1, true>, recurrence_scan_kernel<2, false>, recurrence_scan_kernel<2, true>,
+                               recurrence_scan_kernel<3, false>, recurrence_scan_kernel<3, true>};
     if (smem > allowed[which]) {
         const cudaError_t e = cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         allowed[which] = smem;
     }
     return cw_launch_ordered(kernels[which], grid, dim3(threads), smem, stream, q, ldq, k, ldk, v, ldv, pre, ldp, p0, p1, p2, state,
-                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, H, out, ldo);
+                     state_stride, state_off, slots, tok_seq, q_start, Dk, Dv, heads_per_group, IP, wide, H, out, ldo, q_scale);
+}
+
+// Decays of a gated linear-attention layer from the pre-activations of its decay product, in place (float32):
+//   a[t, c] = sigmoid(pre[t, c])^(1/tau) = exp(log_sigmoid(pre[t, c]) / tau)
+__global__ void __launch_bounds__(256)
+sigmoid_power_decay_kernel(float* __restrict__ pre, int ldp, int N, int C, float inv_tau) {
+    pdl_wait();
+    const long long total = (long long)N * C;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / C), c = (int)(idx - (long long)t * C);
+        float* at = pre + (size_t)t * ldp + c;
+        const float z = *at;
+        const float log_sigmoid = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+        *at = expf(log_sigmoid * inv_tau);
+    }
+}
+
+extern "C" int cw_sigmoid_power_decay(float* pre, int ldp, int N, int C, float inv_tau, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || C <= 0 || ldp < C) return CW_ERR_BAD_SIZE;
+    const long long total = (long long)N * C;
+    const int blocks = (int)min((long long)148 * 8, (total + 255) / 256);
+    return cw_launch_ordered(sigmoid_power_decay_kernel, dim3(blocks), dim3(256), 0, stream, pre, ldp, N, C, inv_tau);
 }
 
 // ---- gated norm in parts ----------------------------------------------------------------------------
-// y [N, C] float32, gate z [N, ldz] float32.  gate_first: u = y silu(z), out = u / rms_part(u) * weight.
-// Otherwise: out = y / rms_part(y) * weight * silu(z).  A block per (row, part); sums in a fixed order.
+// y [N, C] float32, gate z [N, ldz] float32.  mode bit 0 (gate first): u = y gate(z), out = u / rms_part(u) * weight.
+// Otherwise: out = y / rms_part(y) * weight * gate(z).  mode bit 1: gate = sigmoid (else silu).  mode bit 2: every
+// part uses the same weight of one part's width.  A block per (row, part); sums in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ weight,
-                        T* __restrict__ out, int C, int parts, float eps, int gate_first) {
+                        T* __restrict__ out, int C, int parts, float eps, int mode) {
     __shared__ float scratch[33];
     pdl_wait();
+    const int gate_first = mode & 1;
+    const bool plain_sigmoid = mode & 2;
     const int row = blockIdx.x, p = blockIdx.y;
     const int width = C / parts;
     const float* yr = y + (size_t)row * C + (size_t)p * width;
     const float* zr = z + (size_t)row * ldz + (size_t)p * width;
+    const float* wr = weight + ((mode & 4) ? 0 : (size_t)p * width);
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float u = yr[c];
         if (gate_first) {
             const float g = zr[c];
-            u *= g / (1.f + expf(-g));
+            u *= (plain_sigmoid ? 1.f : g) / (1.f + expf(-g));
         }
         ss = fmaf(u, u, ss);
     }
@@ -415,16 +453,16 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float g = zr[c];
-        const float sg = g / (1.f + expf(-g));
+        const float sg = (plain_sigmoid ? 1.f : g) / (1.f + expf(-g));
         const float u = gate_first ? yr[c] * sg : yr[c];
-        float r = u * inv * weight[(size_t)p * width + c];
+        float r = u * inv * wr[c];
         if (!gate_first) r *= sg;
         out[(size_t)row * C + (size_t)p * width + c] = from_f<T>(r);
     }
 }
 
 extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, const float* weight, void* out, int N, int C,
-                                   int parts, float eps, int gate_first, int dtype, cudaStream_t stream) {
+                                   int parts, float eps, int mode, int dtype, cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || C <= 0 || parts <= 0 || C % parts || ldz < C || parts > 65535) return CW_ERR_BAD_SIZE;
     const int width = C / parts;
@@ -433,31 +471,53 @@ extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, cons
     dim3 grid(N, parts);
     if (dtype == 0)
         return cw_launch_ordered(gated_group_norm_kernel<float>, grid, dim3(threads), 0, stream, y, z, ldz, weight, (float*)out, C, parts,
-                         eps, gate_first);
+                         eps, mode);
     if (dtype == 1)
         return cw_launch_ordered(gated_group_norm_kernel<bf16>, grid, dim3(threads), 0, stream, y, z, ldz, weight, (bf16*)out, C, parts,
-                         eps, gate_first);
+                         eps, mode);
     return CW_ERR_BAD_DTYPE;
 }
 
 // ---- activations in place -----------------------------------------------------------------------------
+__device__ __forceinline__ float activation_of(int kind, float z) {
+    if (kind == 0) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 1) return tanhf(z);
+    const float s = 1.f / (1.f + expf(-z));
+    return kind == 2 ? z * s : s;  // silu, sigmoid
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) activation_kernel(T* __restrict__ x, long long n, int kind) {
     pdl_wait();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float z = to_f(x[i]);
-        float r;
-        if (kind == 0)
-            r = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        else
-            r = tanhf(z);
-        x[i] = from_f<T>(r);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = from_f<T>(activation_of(kind, to_f(x[i])));
+}
+
+// the same on the first C columns of rows that are ld apart
+template <typename T>
+__global__ void __launch_bounds__(256) activation_cols_kernel(T* __restrict__ x, int ld, int N, int C, int kind) {
+    pdl_wait();
+    const long long total = (long long)N * C;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / C), c = (int)(i - (long long)t * C);
+        T* at = x + (size_t)t * ld + c;
+        *at = from_f<T>(activation_of(kind, to_f(*at)));
     }
+}
+
+extern "C" int cw_activation_cols(void* x, int ld, int N, int C, int kind, int dtype, cudaStream_t stream) {
+    if (N == 0 || C == 0) return CW_OK;
+    if (N < 0 || C < 0 || ld < C || kind < 0 || kind > 3) return CW_ERR_BAD_SIZE;
+    const long long total = (long long)N * C;
+    const int blocks = (int)min((long long)148 * 8, (total + 255) / 256);
+    if (dtype == 0) return cw_launch_ordered(activation_cols_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ld, N, C, kind);
+    if (dtype == 1) return cw_launch_ordered(activation_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ld, N, C, kind);
+    return CW_ERR_BAD_DTYPE;
 }
 
 extern "C" int cw_activation(void* x, long long n, int kind, int dtype, cudaStream_t stream) {
     if (n == 0) return CW_OK;
-    if (n < 0 || kind < 0 || kind > 1) return CW_ERR_BAD_SIZE;
+    if (n < 0 || kind < 0 || kind > 3) return CW_ERR_BAD_SIZE;
     const int blocks = (int)min((long long)148 * 8, (n + 255) / 256);
     if (dtype == 0) return cw_launch_ordered(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n, kind);
     if (dtype == 1) return cw_launch_ordered(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, n, kind);

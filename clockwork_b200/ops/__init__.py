@@ -113,6 +113,35 @@ def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: 
     return out
 
 
+def scale_add_sinusoid(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, scale: float) -> None:
+    """In place on float32 ``x`` [N, W]: ``x * scale + pe(position)``, ``pe[2i] = sin(position * inv_freq[i])`` and
+    ``pe[2i + 1] = cos`` of the same angle (float32 angles)."""
+    _need(x, torch.float32, "x", 2)
+    _need(positions, torch.int32, "positions", 1)
+    _need(inv_freq, torch.float32, "inv_freq", 1)
+    n, w = x.shape
+    if inv_freq.shape[0] * 2 < w or positions.shape[0] < n:
+        raise ValueError("inv_freq needs an entry per pair of columns, positions one per row")
+    check(library().cw_scale_add_sinusoid(_ptr(x), _ptr(positions), _ptr(inv_freq), float(scale), n, w, _stream()), "scale_add_sinusoid")
+
+
+def pair_rmsnorm_add(resid: torch.Tensor, a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float,
+                     factor: float) -> None:
+    """``resid += factor * (rmsnorm(a) * wa + rmsnorm(b) * wb)``, all float32 [N, W] / [W]."""
+    _need(resid, torch.float32, "resid", 2)
+    n, w = resid.shape
+    for name, t in (("a", a), ("b", b)):
+        _need(t, torch.float32, name, 2)
+        if t.shape != resid.shape:
+            raise ValueError(f"{name} {tuple(t.shape)} does not match the residual {tuple(resid.shape)}")
+    for name, t in (("wa", wa), ("wb", wb)):
+        _need(t, torch.float32, name, 1)
+        if t.shape[0] != w:
+            raise ValueError(f"{name} must have {w} entries")
+    check(library().cw_pair_rmsnorm_add(_ptr(resid), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(eps), float(factor), n, w, _stream()),
+          "pair_rmsnorm_add")
+
+
 class PartialSums:
     """A product that was split over its inner dimension with the splits kept apart: ``slabs`` float32
     [splits, slab_rows, N], of which rows [0, rows) of every slab count; the product is their sum, taken

@@ -34,10 +34,18 @@ _SIGNATURES: dict[str, list] = {
     "cw_shift_mix": [P, P, P, LL, LL, P, P, P, P, I, I, I, I, P],
     "cw_causal_conv": [P, I, P, P, P, LL, LL, P, P, P, P, I, I, I, P],
     "cw_carry_rows": [P, I, P, LL, LL, P, P, P, I, I, I, I, P],
-    "cw_recurrence_scan": [I, P, I, P, I, P, I, P, I, P, P, P, P, LL, LL, P, P, P, I, I, I, I, I, P, I, P],
+    "cw_recurrence_scan": [I, P, I, P, I, P, I, P, I, P, P, P, P, LL, LL, P, P, P, I, I, I, I, I, P, I, F, P],
+    "cw_sigmoid_power_decay": [P, I, I, I, F, P],
+    "cw_activation_cols": [P, I, I, I, I, I, P],
     "cw_recurrence_coefficients": [I, P, I, P, P, P, I, I, P],
     "cw_gated_group_norm": [P, P, I, P, P, I, I, I, F, I, I, P],
     "cw_activation": [P, LL, I, I, P],
+    # attention over a window of rows [key | value] (csrc/window_attention.cu); absolute positions and the sum of two normed
+    # contributions (csrc/embed_norm.cu)
+    "cw_store_rows": [P, I, I, I, P, P, I, LL, I, P, P],
+    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, I, P, I, P, P],
+    "cw_scale_add_sinusoid": [P, P, P, F, I, I, P],
+    "cw_pair_rmsnorm_add": [P, P, P, P, P, F, F, I, I, P],
     # products in groups and the mixture of experts (csrc/grouped_gemm.cu)
     "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, I, P],
     "cw_grouped_gemm_set_mma": [I],

@@ -12,8 +12,9 @@ import torch
 from . import _need, _ptr, _stream, dtype_code
 from .library import check, library
 
-FORM_CHANNEL_DECAY, FORM_STEP_SIZE = 0, 1
-ACT_GELU_TANH, ACT_TANH = 0, 1
+FORM_CHANNEL_DECAY, FORM_STEP_SIZE, FORM_CHANNEL_DECAY_AFTER, FORM_HEAD_DECAY = 0, 1, 2, 3
+ACT_GELU_TANH, ACT_TANH, ACT_SILU, ACT_SIGMOID = 0, 1, 2, 3
+GATE_SILU, GATE_SIGMOID = 0, 1
 
 
 def _state_args(view) -> tuple:
@@ -65,12 +66,15 @@ def carry_rows(x: torch.Tensor, rows: int, view, offset: int, ctx) -> None:
 
 
 def recurrence_scan(form: int, q, k, v, pre, p0, p1, p2, view, offset: int, ctx, heads: int, dk: int, dv: int,
-                    heads_per_group: int = 1) -> torch.Tensor:
-    """float32 [N, heads*dv].  ``q``, ``k`` [N, groups*dk], ``v`` [N, heads*dv], ``pre`` [N, heads*dk] (form 0) or
-    [N, heads] (form 1): float32, unit column stride, any row stride.  The state piece at ``offset`` holds
-    heads*dk*dv numbers.  Form 0 turns ``pre`` into the decays in place (it is a product's output that nothing
-    else reads)."""
+                    heads_per_group: int = 1, q_scale: float = 1.0) -> torch.Tensor:
+    """float32 [N, heads*dv].  ``q``, ``k`` [N, groups*dk], ``v`` [N, heads*dv], ``pre`` [N, heads*dk] (forms 0 and 2) or
+    [N, heads] (form 1) or None (form 3): float32, unit column stride, any row stride.  The state piece at ``offset``
+    holds heads*dk*dv numbers.  Form 0 turns ``pre`` into the decays in place (it is a product's output that nothing
+    else reads); form 2 takes ``pre`` as the decays themselves (``sigmoid_power_decay``); form 3 takes a constant
+    decay per head in ``p0``.  ``q_scale`` multiplies the outputs of forms 2 and 3."""
     for name, t in (("q", q), ("k", k), ("v", v), ("pre", pre)):
+        if t is None and name == "pre" and form == FORM_HEAD_DECAY:
+            continue
         if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise ValueError(f"{name} must be float32 [N, *] with unit column stride")
     n = v.shape[0]
@@ -84,28 +88,53 @@ def recurrence_scan(form: int, q, k, v, pre, p0, p1, p2, view, offset: int, ctx,
     if form == FORM_CHANNEL_DECAY:
         check(library().cw_recurrence_coefficients(form, _ptr(pre), ld(pre), _ptr(p0), None, None, n, heads * dk, _stream()),
               "recurrence_coefficients")
-    else:
+    elif form == FORM_STEP_SIZE:
         coef = torch.empty((n, 2 * heads), dtype=torch.float32, device=v.device)
         check(library().cw_recurrence_coefficients(form, _ptr(pre), ld(pre), _ptr(p0), _ptr(p1), _ptr(coef), n, heads, _stream()),
               "recurrence_coefficients")
         pre = coef
-    check(library().cw_recurrence_scan(form, _ptr(q), ld(q), _ptr(k), ld(k), _ptr(v), ld(v), _ptr(pre), ld(pre), _ptr(p0), _ptr(p1),
-                                       _ptr(p2), state, stride, offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs,
-                                       heads, dk, dv, heads_per_group, _ptr(out), heads * dv, _stream()), "recurrence_scan")
+    check(library().cw_recurrence_scan(form, _ptr(q), ld(q), _ptr(k), ld(k), _ptr(v), ld(v), _ptr(pre), 0 if pre is None else ld(pre),
+                                       _ptr(p0), _ptr(p1), _ptr(p2), state, stride, offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start),
+                                       ctx.num_seqs, heads, dk, dv, heads_per_group, _ptr(out), heads * dv, float(q_scale), _stream()),
+          "recurrence_scan")
     return out
 
 
+def sigmoid_power_decay_(pre: torch.Tensor, tau: float) -> torch.Tensor:
+    """In place: ``sigmoid(pre)^(1/tau)``, the decays of a gated linear-attention layer.  float32 [N, C], any row stride."""
+    if pre.dtype != torch.float32 or pre.dim() != 2 or pre.stride(1) != 1:
+        raise ValueError("pre must be float32 [N, C] with unit column stride")
+    n, c = pre.shape
+    check(library().cw_sigmoid_power_decay(_ptr(pre), pre.stride(0) if n > 1 else max(pre.stride(0), c), n, c, 1.0 / float(tau),
+                                           _stream()), "sigmoid_power_decay")
+    return pre
+
+
+def activation_cols_(x: torch.Tensor, cols: int, kind: int) -> torch.Tensor:
+    """In place on the first ``cols`` columns of every row of ``x`` [N, C] (unit column stride)."""
+    if x.dim() != 2 or x.stride(1) != 1 or not 0 <= cols <= x.shape[1]:
+        raise ValueError("x must be [N, C] with unit column stride and cols within C")
+    n = x.shape[0]
+    check(library().cw_activation_cols(_ptr(x), x.stride(0) if n > 1 else max(x.stride(0), x.shape[1]), n, cols, kind,
+                                       dtype_code(x.dtype), _stream()), "activation_cols")
+    return x
+
+
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float, gate_first: bool,
-                     out_dtype: torch.dtype) -> torch.Tensor:
-    """``gate_first``: norm_parts(y * silu(z)) * weight; else norm_parts(y) * weight * silu(z).  y, z float32."""
+                     out_dtype: torch.dtype, gate: int = GATE_SILU, shared_weight: bool = False) -> torch.Tensor:
+    """``gate_first``: norm_parts(y * gate(z)) * weight; else norm_parts(y) * weight * gate(z).  y, z float32.
+    ``gate``: silu or sigmoid.  ``shared_weight``: ``weight`` has one part's width and every part uses it."""
     _need(y, torch.float32, "y", 2)
     if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1:
         raise ValueError("z must be float32 [N, C] with unit column stride")
     _need(weight, torch.float32, "weight", 1)
     n, c = y.shape
+    if weight.shape[0] != (c // parts if shared_weight else c):
+        raise ValueError(f"weight of {weight.shape[0]} for {parts} parts of {c} columns")
     out = torch.empty((n, c), dtype=out_dtype, device=y.device)
+    mode = (1 if gate_first else 0) | (2 if gate == GATE_SIGMOID else 0) | (4 if shared_weight else 0)
     check(library().cw_gated_group_norm(_ptr(y), _ptr(z), z.stride(0) if n > 1 else max(z.stride(0), c), _ptr(weight), _ptr(out), n, c,
-                                        parts, float(eps), 1 if gate_first else 0, dtype_code(out_dtype), _stream()),
+                                        parts, float(eps), mode, dtype_code(out_dtype), _stream()),
           "gated_group_norm")
     return out
 

@@ -1,0 +1,81 @@
+"""Python faces of ``csrc/window_attention.cu``: the row copy that stores a token's keys and values, and
+attention over a sliding window of cache rows ``[key | value]`` with the score variants of that file."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _need, _ptr, _stream, dtype_code
+from .library import check, library
+
+SPLIT_MAX_PARTS = 16
+SPLIT_BELOW_TOKENS = 64  # windows are cut only in steps of fewer tokens than this
+_scratch: dict[tuple, torch.Tensor] = {}  # (device index, floats per token and part) -> the partial sums of cut windows
+
+
+def _partial_sums(device, heads: int, dv: int) -> torch.Tensor:
+    """Room for the partial sums of the largest step whose windows are cut, made once per size and never replaced
+    (captured steps point at it)."""
+    per = heads * dv + 2 * heads
+    key = (torch.device(device).index or 0, per)
+    have = _scratch.get(key)
+    if have is None:
+        have = _scratch[key] = torch.empty(SPLIT_BELOW_TOKENS * SPLIT_MAX_PARTS * per, dtype=torch.float32, device=device)
+    return have
+
+
+def store_rows(src: torch.Tensor, col0: int, width: int, cache_rows: torch.Tensor, slots: torch.Tensor, status: torch.Tensor) -> None:
+    """``cache_rows[slots[n]] = src[n, col0 : col0 + width]`` for every token n with a slot (< 0: none)."""
+    if src.dim() != 2 or src.stride(1) != 1:
+        raise ValueError("src must be [N, C] with unit column stride")
+    _need(cache_rows, src.dtype, "cache")
+    _need(slots, torch.int32, "slots", 1)
+    n = src.shape[0]
+    total = cache_rows.numel() // width
+    check(library().cw_store_rows(_ptr(src), src.stride(0) if n > 1 else max(src.stride(0), src.shape[1]), col0, width, _ptr(cache_rows),
+                                  _ptr(slots), n, total, dtype_code(src.dtype), _ptr(status), _stream()), "store_rows")
+
+
+def window_parts(num_tokens: int, window: int, dtype: torch.dtype) -> int:
+    """In how many pieces a token's window is cut: one, unless a bfloat16 step has so few tokens that whole
+    windows per thread block would leave most of the GPU idle.  (float32 runs never cut: their results do not
+    depend on the step's size to the last bit.)"""
+    if dtype != torch.bfloat16 or num_tokens >= SPLIT_BELOW_TOKENS or window <= 256:
+        return 1
+    return max(1, min(SPLIT_MAX_PARTS, window // 128, 128 // max(1, num_tokens)))
+
+
+def reserve_window_scratch(device, heads: int, dv: int) -> None:
+    _partial_sums(device, heads, dv)
+
+
+def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor,
+                     tok_seq: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, window: int, scale: float,
+                     head_scale: torch.Tensor | None, talk: torch.Tensor | None, head_bias: torch.Tensor | None,
+                     sigmoid_weights: bool, status: torch.Tensor, parts: int = 1) -> torch.Tensor:
+    """[N, heads*dv] in ``q``'s dtype.  ``q`` [N, >= heads*dk] (queries in the leading columns, unit column stride);
+    ``cache_rows`` [pages, page_size, kv_heads, dk + dv]; the step's tokens are already stored there."""
+    if q.dim() != 2 or q.stride(1) != 1 or q.shape[1] < heads * dk:
+        raise ValueError("q must be [N, >= heads*dk] with unit column stride")
+    _need(cache_rows, q.dtype, "cache", 4)
+    if tuple(cache_rows.shape[2:]) != (kv_heads, dk + dv):
+        raise ValueError(f"cache rows {tuple(cache_rows.shape)} are not [pages, page_size, {kv_heads}, {dk + dv}]")
+    _need(block_tables, torch.int32, "block_tables", 2)
+    for name, t, size in (("head_scale", head_scale, heads), ("talk", talk, heads * heads), ("head_bias", head_bias, heads)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != size:
+                raise ValueError(f"{name} has {t.numel()} numbers, {size} expected")
+    n = q.shape[0]
+    out = torch.empty((n, heads * dv), dtype=q.dtype, device=q.device)
+    partial = None
+    if parts > 1:
+        if n >= SPLIT_BELOW_TOKENS or parts > SPLIT_MAX_PARTS:
+            raise ValueError(f"windows are cut in at most {SPLIT_MAX_PARTS} parts and in steps of fewer than {SPLIT_BELOW_TOKENS} tokens")
+        partial = _partial_sums(q.device, heads, dv)
+    check(library().cw_window_attention(
+        _ptr(q), q.stride(0) if n > 1 else max(q.stride(0), q.shape[1]), _ptr(cache_rows), _ptr(block_tables), block_tables.shape[1],
+        cache_rows.shape[1], cache_rows.shape[0], _ptr(positions), _ptr(tok_seq), n, heads, kv_heads, dk, dv, int(window), float(scale),
+        _ptr(head_scale), _ptr(talk), _ptr(head_bias), 1 if sigmoid_weights else 0, _ptr(out), parts, _ptr(partial),
+        dtype_code(q.dtype), _ptr(status), _stream()), "window_attention")
+    return out

@@ -1,7 +1,10 @@
 """Parts: norms, position encodings, mixers, feed-forwards, blocks, and the model made of them.
 Importing this package registers the built-in kinds."""
 
-from . import attention, block, feedforward, latent_attention, parallel_block, rmsnorm, rotary, state_mixers, swiglu  # noqa: F401  (registration)
+from . import (  # noqa: F401  (registration)
+    attention, block, feedforward, latent_attention, parallel_block, rmsnorm, rotary, side_by_side, state_mixers, swiglu,
+    window_attention,
+)
 from .base import (
     Block, FeedForward, Mixer, Norm, PagedKVNeed, PagedView, Part, PositionEncoding,
     ResidualStream, SlotStateNeed, StateView, StepContext,

@@ -219,8 +219,16 @@ class PositionEncoding(Part):
 class Mixer(Part):
     takes_half_normed = False  # True: ``x`` may be an ``ops.gemm.RowScaled`` (it only feeds matrix products)
 
-    def cache_need(self) -> PagedKVNeed | SlotStateNeed | None:
+    def cache_need(self) -> PagedKVNeed | SlotStateNeed | tuple | None:
+        """What the mixer keeps per request.  A mixer made of several (``side_by_side``) returns a tuple of
+        needs, at most one of them pages and at most one a state slot, and is handed a tuple of views in the
+        same order."""
         return None
+
+    def mix(self, ctx: StepContext, x: torch.Tensor, view) -> torch.Tensor:
+        """The mixer's output as float32 [N, hidden], added to nothing: what a mixer that combines several
+        (``side_by_side``) asks of each.  Optional: a mixer that only ever stands alone need not have it."""
+        raise NotImplementedError(f"{type(self).__name__} cannot be used inside another mixer")
 
     def forward(self, ctx: StepContext, x: torch.Tensor, view, stream: ResidualStream) -> torch.Tensor | None:
         raise NotImplementedError

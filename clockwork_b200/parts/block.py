@@ -14,17 +14,22 @@ from .registry import build_part, register_block
 
 
 class PreNormResidualBlock(Block):
+    NAMES = ("input_layernorm", "self_attn", "post_attention_layernorm", "mlp")  # first norm, mixer, second norm, feed-forward
+
     def __init__(self, layer: LayerSpec, dtype, device) -> None:
         self.layer = layer
         self.prefix = layer.prefix
         self.dtype, self.device = dtype, device
-        self.mixer_norm = build_part("norm", layer.mixer_norm, f"{layer.prefix}.input_layernorm", dtype, device)
-        self.mixer = build_part("mixer", layer.mixer, f"{layer.prefix}.self_attn", dtype, device)
-        self.ffn_norm = build_part("norm", layer.ffn_norm, f"{layer.prefix}.post_attention_layernorm", dtype, device)
-        self.ffn = build_part("ffn", layer.ffn, f"{layer.prefix}.mlp", dtype, device)
+        norm1, mixer, norm2, ffn = self.NAMES
+        self.mixer_norm = build_part("norm", layer.mixer_norm, f"{layer.prefix}.{norm1}", dtype, device)
+        self.mixer = build_part("mixer", layer.mixer, f"{layer.prefix}.{mixer}", dtype, device)
+        self.ffn_norm = self.ffn = None  # a layer without a feed-forward names the kind ``none``
+        if layer.ffn.kind != "none":
+            self.ffn_norm = build_part("norm", layer.ffn_norm, f"{layer.prefix}.{norm2}", dtype, device)
+            self.ffn = build_part("ffn", layer.ffn, f"{layer.prefix}.{ffn}", dtype, device)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return (self.mixer_norm, self.mixer) + (() if self.ffn is None else (self.ffn_norm, self.ffn))
 
     @property
     def graph_safe(self) -> bool:
@@ -49,12 +54,22 @@ class PreNormResidualBlock(Block):
 
     def forward(self, ctx: StepContext, stream: ResidualStream, view, following_norm=None) -> None:
         x = self._normed(self.mixer_norm, self.mixer, stream, ctx.status)
-        stream.next_norm = self.ffn_norm  # what the mixer's output product may begin
+        stream.next_norm = self.ffn_norm if self.ffn is not None else following_norm  # what the mixer's output product may begin
         stream.push(self.mixer.forward(ctx, x, view, stream))
+        if self.ffn is None:
+            stream.next_norm = None
+            return
         x = self._normed(self.ffn_norm, self.ffn, stream, ctx.status)
         stream.next_norm = following_norm
         stream.push(self.ffn.forward(ctx, x, stream))
         stream.next_norm = None
 
 
+class ShortNamePreNormBlock(PreNormResidualBlock):
+    """The same arrangement with the tensor prefixes ``<layer>.norm1``, ``<layer>.mix``, ``<layer>.norm2``, ``<layer>.mlp``."""
+
+    NAMES = ("norm1", "mix", "norm2", "mlp")
+
+
 register_block("prenorm_residual", PreNormResidualBlock, replace=True)
+register_block("prenorm_residual_short", ShortNamePreNormBlock, replace=True)

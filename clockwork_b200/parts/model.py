@@ -29,6 +29,11 @@ class DecoderModel:
         self.device = torch.device(device)
         self.blocks = [build_block(layer, dtype, self.device) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix, dtype, self.device)
+        self.absolute_positions = None
+        if spec.absolute_positions is not None:
+            self.absolute_positions = build_part("position", spec.absolute_positions, "", dtype, self.device)
+        elif spec.embedding_scale != 1.0:
+            raise ValueError("an embedding scale needs a position part that applies it (absolute_positions)")
         self.embedding: torch.Tensor | None = None
         self.head: Linear | None = None
 
@@ -51,7 +56,8 @@ class DecoderModel:
 
     def graph_safe(self) -> bool:
         """Whether a step of this model may be captured in a CUDA graph."""
-        return all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
+        return (all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
+                and (self.absolute_positions is None or self.absolute_positions.graph_safe))
 
     def graph_safe_portions(self) -> bool:
         """Whether a step of this model that holds prompt portions may be captured in a CUDA graph."""
@@ -62,6 +68,8 @@ class DecoderModel:
         for block in self.blocks:
             yield from block.parts()
         yield self.final_norm
+        if self.absolute_positions is not None:
+            yield self.absolute_positions
 
     def step_scalars(self) -> dict:
         """The per-step device scalars that the model's parts declare (``Part.step_scalars``), by name."""
@@ -134,6 +142,8 @@ class DecoderModel:
         # (kernels of a step read its inputs before they wait for their predecessors; when a kernel has
         # only just written those inputs, the first kernel here must not start before it has finished)
         stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device))
+        if self.absolute_positions is not None:
+            self.absolute_positions.add_to_embedding(stream.residual, ctx.positions, self.spec.embedding_scale)
         schedule = self.spec.schedule
         for i, step in enumerate(schedule):
             view = ctx.views.get(step.resolved_cache_layer())

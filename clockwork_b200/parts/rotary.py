@@ -60,5 +60,24 @@ class NoPosition(PositionEncoding):
                            num_heads, num_kv_heads, head_dim, 0, ctx.status, write_cache=True)
 
 
+class SinusoidalAbsolute(PositionEncoding):
+    """A vector per position added to the embedding rows: entry 2i is ``sin(t * base^(-2i/size))`` and entry
+    2i+1 the cosine of the same angle (float32 angles).  Parameters: ``size`` (the model's width), ``base``.  The
+    model calls ``add_to_embedding`` once per step, with the scale of the embedding rows."""
+
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        self.size, self.base = int(spec["size"]), float(spec.get("base", 10000.0))
+        exponents = torch.arange(0, self.size, 2, dtype=torch.float64) / self.size
+        self.inv_freq = (self.base ** -exponents).to(torch.float32).to(device)
+
+    def add_to_embedding(self, x: torch.Tensor, positions: torch.Tensor, scale: float) -> None:
+        ops.scale_add_sinusoid(x, positions, self.inv_freq, scale)
+
+
+register_position("sinusoidal_absolute", SinusoidalAbsolute, replace=True)
 register_position("rope_neox", RotaryNeox, replace=True)
 register_position("none", NoPosition, replace=True)

@@ -1,0 +1,80 @@
+"""Two mixers side by side: both read the same input, each output is RMS-normed over the model's width
+with a weight of its own, and the mixer's result is ``factor`` times their sum:
+
+    out = factor * (n(left(h)) g_left + n(right(h)) g_right),   n(y) = y / sqrt(mean(y^2) + eps)
+
+Parameters: ``hidden_size, eps, factor`` (0.5: half the sum), ``left`` and ``right`` (the ``PartSpec`` of any
+registered mixer that has ``mix``).  Tensors: the mixers' own under ``<prefix>.left`` and ``<prefix>.right``, and the
+two weights ``left.out`` and ``right.out`` [hidden].  What the two keep per request is asked for as a tuple (pages
+of the one, a state slot of the other); the norms and the sum into the residual are one float32 kernel.
+"""
+
+from __future__ import annotations
+
+from .. import ops
+from ..weights.decl import TensorDecl
+from .base import Mixer, PagedKVNeed, ResidualStream, SlotStateNeed, StepContext
+from .registry import build_part, register_mixer
+
+
+class SideBySide(Mixer):
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.eps = float(p["eps"])
+        self.factor = float(p.get("factor", 0.5))
+        self.left = build_part("mixer", p["left"], self.name("left"), dtype, device)
+        self.right = build_part("mixer", p["right"], self.name("right"), dtype, device)
+        self.graph_safe = bool(self.left.graph_safe and self.right.graph_safe)
+        self.graph_safe_portions = bool(self.left.graph_safe_portions and self.right.graph_safe_portions)
+        self.left_weight = self.right_weight = None
+        needs = [m.cache_need() for m in (self.left, self.right)]
+        if any(isinstance(n, tuple) for n in needs):
+            raise ValueError("a mixer inside side_by_side must keep one thing per request at most")
+        for kind in (PagedKVNeed, SlotStateNeed):
+            if sum(isinstance(n, kind) for n in needs) > 1:
+                raise ValueError(f"both mixers of {prefix!r} keep {kind.__name__}: one layer has one of each at most")
+        self._needs = needs
+
+    def cache_need(self):
+        kept = tuple(n for n in self._needs if n is not None)
+        return kept or None
+
+    def _views(self, view):
+        """The views of the two mixers from the tuple that follows ``cache_need``'s order."""
+        views = iter(view if isinstance(view, tuple) else (() if view is None else (view,)))
+        return tuple(next(views) if n is not None else None for n in self._needs)
+
+    # hooks of captured steps: whatever either mixer declares
+    def step_scalars(self):
+        return {**self.right.step_scalars(), **self.left.step_scalars()}
+
+    def step_arrays(self, *args, **kwargs):
+        return {**self.right.step_arrays(*args, **kwargs), **self.left.step_arrays(*args, **kwargs)}
+
+    def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
+        self.left.reserve_for_steps(max_seqs, max_ctx)
+        self.right.reserve_for_steps(max_seqs, max_ctx)
+
+    def tensor_decls(self):
+        yield from self.left.tensor_decls()
+        yield from self.right.tensor_decls()
+        yield TensorDecl(self.name("left.out"), (self.hidden_size,), "vector", "norm")
+        yield TensorDecl(self.name("right.out"), (self.hidden_size,), "vector", "norm")
+
+    def load_weights(self, fetch) -> None:
+        self.left.load_weights(fetch)
+        self.right.load_weights(fetch)
+        self.left_weight = fetch(self.name("left.out")).contiguous()
+        self.right_weight = fetch(self.name("right.out")).contiguous()
+
+    def forward(self, ctx: StepContext, x, view, stream: ResidualStream):
+        left_view, right_view = self._views(view)
+        a = self.left.mix(ctx, x, left_view)
+        b = self.right.mix(ctx, x, right_view)
+        ops.pair_rmsnorm_add(stream.residual_after_flush(), a, b, self.left_weight, self.right_weight, self.eps, self.factor)
+        return None
+
+
+register_mixer("side_by_side", SideBySide, replace=True)

@@ -17,8 +17,21 @@ per head and key channel.  Per head ``o = (S + diag(u) k v^T)^T r`` and then ``S
 Each head's o is divided by its root mean square, times ``norm``, times the gate, and goes through ``o``.
 The state slot holds S of every head and the previous token's input.
 
-Both run the recurrence itself, the decays, step sizes and norms in float32 in either run precision;
-the products that feed them write float32.
+``gated_linear`` (linear attention with a decay per key channel that the input chooses).  Parameters:
+``hidden_size, heads, dim, vdim, tau, eps``; the inner size of the decay's two products is whatever the
+checkpoint's ``a1`` has (``decay_rank`` only sizes random weights).  ``q = (W_q x) dim^(-1/2)``, ``k, v`` plain
+products, ``a = sigmoid(W_a2 (W_a1 x) + b)^(1/tau)`` per head and key channel; per head ``S <- diag(a) S + k v^T``,
+``o = S^T q`` (after the update).  Each head's o is divided by its root mean square over vdim, times ``norm`` (one
+weight of vdim entries for all heads), times ``silu(W_g x)``, and goes through ``o``.  The state slot holds S.
+
+``decay_linear`` (linear attention with one constant decay per head).  Parameters: ``hidden_size, heads, dim,
+vdim, decay`` (a number per head), ``eps``.  ``q, k, v = silu(W_q x), silu(W_k x), silu(W_v x)``; per head
+``S <- decay_h S + k v^T``, ``o = S^T q``.  The heads' outputs together are divided by their root mean square, times
+``norm``, times ``sigmoid(W_g x)``, and go through ``o``.  The state slot holds S.
+
+All run the recurrence itself, the decays, step sizes and norms in float32 in either run precision;
+the products that feed them write float32.  ``mix`` returns the output product as float32 for a mixer that
+stands beside another (``side_by_side``).
 """
 
 from __future__ import annotations
@@ -145,5 +158,104 @@ class WkvMixer(Mixer):
         return self.o.add_or_defer(out, stream)
 
 
+class _LinearAttention(Mixer):
+    """What the two linear-attention mixers share: one product for ``[q | k | v | gate]`` with float32 output, the
+    state of heads*dim*vdim numbers, and the output product."""
+
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.dim, self.vdim = int(p["heads"]), int(p["dim"]), int(p["vdim"])
+        self.eps = float(p["eps"])
+        if min(self.heads, self.dim, self.vdim) <= 0:
+            raise ValueError("heads, dim and vdim must be positive")
+        self.qk, self.inner = self.heads * self.dim, self.heads * self.vdim
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.heads * self.dim * self.vdim,))
+
+    def _projection_decls(self):
+        h = self.hidden_size
+        for s, out in (("q", self.qk), ("k", self.qk), ("v", self.inner), ("g", self.inner)):
+            yield TensorDecl(self.name(s), (out, h), "matrix", "linear")
+        yield TensorDecl(self.name("o"), (h, self.inner), "matrix", "linear")
+
+    def _load_projections(self, fetch) -> None:
+        self.w_in = Linear(torch.cat([fetch(self.name(s)) for s in ("q", "k", "v", "g")], dim=0).contiguous())
+        self.o = Linear(fetch(self.name("o")))
+
+    def _split(self, proj):
+        qk, inner = self.qk, self.inner
+        return proj[:, :qk], proj[:, qk : 2 * qk], proj[:, 2 * qk : 2 * qk + inner], proj[:, 2 * qk + inner :]
+
+    def mix(self, ctx: StepContext, x, view: StateView):
+        return self.o.to_float32(self._gated_output(ctx, x, view))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        return self.o.add_or_defer(self._gated_output(ctx, x, view), stream)
+
+
+class GatedLinearMixer(_LinearAttention):
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        self.tau = float(spec["tau"])
+        self.decay_rank = int(spec.get("decay_rank") or 16)
+        if self.tau <= 0:
+            raise ValueError("tau must be positive")
+
+    def tensor_decls(self):
+        yield from self._projection_decls()
+        yield TensorDecl(self.name("a1"), (self.decay_rank, self.hidden_size), "matrix", "linear", free_dims=(0,))
+        yield TensorDecl(self.name("a2"), (self.qk, self.decay_rank), "matrix", "linear", free_dims=(1,))
+        yield TensorDecl(self.name("a2.b"), (self.qk,), "vector", "bias")
+        yield TensorDecl(self.name("norm"), (self.vdim,), "vector", "norm")
+
+    def load_weights(self, fetch) -> None:
+        self._load_projections(fetch)
+        self.a1 = Linear(fetch(self.name("a1")))
+        self.a2 = Linear(fetch(self.name("a2")), fetch(self.name("a2.b")))
+        if self.a1.out_features != self.a2.in_features:
+            raise ValueError(f"{self.name('a1')} has {self.a1.out_features} rows, {self.name('a2')} {self.a2.in_features} columns")
+        self.norm_w = fetch(self.name("norm")).contiguous()
+
+    def _gated_output(self, ctx: StepContext, x, view: StateView):
+        q, k, v, g = self._split(self.w_in.to_float32(x))
+        decay = rec_ops.sigmoid_power_decay_(self.a2.to_float32(self.a1(x)), self.tau)
+        o = rec_ops.recurrence_scan(rec_ops.FORM_CHANNEL_DECAY_AFTER, q=q, k=k, v=v, pre=decay, p0=None, p1=None, p2=None, view=view,
+                                    offset=0, ctx=ctx, heads=self.heads, dk=self.dim, dv=self.vdim, q_scale=self.dim ** -0.5)
+        return rec_ops.gated_group_norm(o, g, self.norm_w, self.heads, self.eps, False, self.dtype, gate=rec_ops.GATE_SILU,
+                                        shared_weight=True)
+
+
+class DecayLinearMixer(_LinearAttention):
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        decay = [float(d) for d in spec["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"decay has {len(decay)} numbers for {self.heads} heads")
+        self.decay = torch.tensor(decay, dtype=torch.float32).to(device)
+
+    def tensor_decls(self):
+        yield from self._projection_decls()
+        yield TensorDecl(self.name("norm"), (self.inner,), "vector", "norm")
+
+    def load_weights(self, fetch) -> None:
+        self._load_projections(fetch)
+        self.norm_w = fetch(self.name("norm")).contiguous()
+
+    def _gated_output(self, ctx: StepContext, x, view: StateView):
+        proj = rec_ops.activation_cols_(self.w_in.to_float32(x), 2 * self.qk + self.inner, rec_ops.ACT_SILU)  # q, k, v; not the gate
+        q, k, v, g = self._split(proj)
+        o = rec_ops.recurrence_scan(rec_ops.FORM_HEAD_DECAY, q=q, k=k, v=v, pre=None, p0=self.decay, p1=None, p2=None, view=view,
+                                    offset=0, ctx=ctx, heads=self.heads, dk=self.dim, dv=self.vdim)
+        return rec_ops.gated_group_norm(o, g, self.norm_w, 1, self.eps, False, self.dtype, gate=rec_ops.GATE_SIGMOID)
+
+
+register_mixer("gated_linear", GatedLinearMixer, replace=True)
+register_mixer("decay_linear", DecayLinearMixer, replace=True)
 register_mixer("mamba2", Mamba2Mixer, replace=True)
 register_mixer("wkv", WkvMixer, replace=True)

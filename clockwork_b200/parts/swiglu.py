@@ -1,7 +1,8 @@
 """SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``, no biases.
 
 Reference: ``clockwork/engine/model.py:52-63``.  Parameters: ``hidden_size, intermediate_size``.
-Tensors: ``gate_proj.weight`` [I, H], ``up_proj.weight`` [I, H], ``down_proj.weight`` [H, I].
+Tensors: ``gate_proj.weight`` [I, H], ``up_proj.weight`` [I, H], ``down_proj.weight`` [H, I]; with the
+optional parameter ``names`` = (gate, up, down) the three tensors have those names behind the prefix instead.
 The gate and up products and the activation run as one kernel; the down product adds into the
 float32 residual.
 """
@@ -24,19 +25,22 @@ class SwiGLU(FeedForward):
         super().__init__(spec, prefix, dtype, device)
         self.hidden_size = int(spec["hidden_size"])
         self.intermediate_size = int(spec["intermediate_size"])
+        self.names = tuple(spec.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         self.w_gate = self.w_up = None
         self.down: Linear | None = None
 
     def tensor_decls(self):
         h, i = self.hidden_size, self.intermediate_size
-        yield TensorDecl(self.name("gate_proj.weight"), (i, h), "matrix", "linear")
-        yield TensorDecl(self.name("up_proj.weight"), (i, h), "matrix", "linear")
-        yield TensorDecl(self.name("down_proj.weight"), (h, i), "matrix", "linear")
+        gate, up, down = self.names
+        yield TensorDecl(self.name(gate), (i, h), "matrix", "linear")
+        yield TensorDecl(self.name(up), (i, h), "matrix", "linear")
+        yield TensorDecl(self.name(down), (h, i), "matrix", "linear")
 
     def load_weights(self, fetch) -> None:
-        self.w_gate = fetch(self.name("gate_proj.weight"))
-        self.w_up = fetch(self.name("up_proj.weight"))
-        self.down = Linear(fetch(self.name("down_proj.weight")))
+        gate, up, down = self.names
+        self.w_gate = fetch(self.name(gate))
+        self.w_up = fetch(self.name(up))
+        self.down = Linear(fetch(self.name(down)))
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):
         act = gemm_ops.swiglu(x, self.w_gate, self.w_up)

@@ -1,0 +1,121 @@
+"""Grouped-query attention over a sliding window, for layers whose keys and values have different sizes and
+whose scores are not just a scaled dot product.
+
+Parameters: ``hidden_size, heads, kv_heads, dim`` (query/key size per head), ``vdim`` (value size per head),
+``window`` (position t sees positions j with 0 <= t - j < window), ``scale``, and the switches
+
+* ``bias``: q, k, v and the output product have biases (tensors ``q.b, k.b, v.b, o.b``);
+* ``head_scale``: the score of head h is multiplied by ``temp[h]``;
+* ``talk``: the heads' scores are mixed before they become weights, ``s_h <- sum_g talk[h, g] s_g``;
+* ``head_bias``: ``pb[h]`` is added to the (mixed) score;
+* ``weights``: ``"softmax"`` over the visible keys, or ``"sigmoid"`` of each score on its own (not normalised).
+
+Positions do not enter the scores.  Tensors: ``q`` [heads*dim, hidden], ``k`` [kv_heads*dim, hidden], ``v``
+[kv_heads*vdim, hidden], ``o`` [hidden, heads*vdim], and those the switches name.
+
+The cache keeps one row ``[key | value]`` per token and key/value head (``PagedKVNeed(planes=1)`` with rows of
+``dim + vdim``), in a page group that gives pages back behind the window.  At load the rows of k and v are
+interleaved head by head behind q, so that one product yields ``[q | k_0 v_0 | k_1 v_1 ..]`` per token and the
+cache write is a copy of the row's tail.  Scores, weights and weighted sums are float32 in either run precision.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import window as window_ops
+from ..weights.decl import TensorDecl
+from .base import Mixer, PagedKVNeed, PagedView, ResidualStream, StepContext
+from .linear import Linear
+from .registry import register_mixer
+
+
+class WindowAttention(Mixer):
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.window = int(p["window"])
+        self.scale = float(p["scale"])
+        self.bias = bool(p.get("bias", False))
+        self.has_head_scale, self.has_talk, self.has_head_bias = (bool(p.get(k, False)) for k in ("head_scale", "talk", "head_bias"))
+        self.weights = str(p.get("weights", "softmax"))
+        if self.weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"weights must be 'softmax' or 'sigmoid', got {self.weights!r}")
+        if self.heads <= 0 or self.kv_heads <= 0 or self.heads % self.kv_heads:
+            raise ValueError(f"heads {self.heads} not a multiple of kv_heads {self.kv_heads}")
+        if min(self.dim, self.vdim, self.window) <= 0:
+            raise ValueError("dim, vdim and window must be positive")
+        self.row = self.dim + self.vdim
+        self.qkv: Linear | None = None
+        self.o: Linear | None = None
+        self.head_scale = self.talk = self.head_bias = None
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.kv_heads, self.row, self.window, planes=1)
+
+    def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
+        if self.device.type == "cuda":
+            window_ops.reserve_window_scratch(self.device, self.heads, self.vdim)
+
+    def tensor_decls(self):
+        h = self.hidden_size
+        for name, out in (("q", self.heads * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)):
+            yield TensorDecl(self.name(name), (out, h), "matrix", "linear")
+            if self.bias:
+                yield TensorDecl(self.name(f"{name}.b"), (out,), "vector", "bias")
+        if self.has_head_scale:
+            yield TensorDecl(self.name("temp"), (self.heads,), "vector", "norm")
+        if self.has_talk:
+            yield TensorDecl(self.name("talk"), (self.heads, self.heads), "vector", "norm")
+        if self.has_head_bias:
+            yield TensorDecl(self.name("pb"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("o"), (h, self.heads * self.vdim), "matrix", "linear")
+        if self.bias:
+            yield TensorDecl(self.name("o.b"), (h,), "vector", "bias")
+
+    def _rows_by_kv_head(self, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """k [G*dim, ..] and v [G*vdim, ..] as [G*(dim + vdim), ..]: head by head, the key's rows before the value's."""
+        g = self.kv_heads
+        tail = k.shape[1:]
+        return torch.cat([k.reshape(g, self.dim, *tail), v.reshape(g, self.vdim, *tail)], dim=1).reshape(g * self.row, *tail)
+
+    def load_weights(self, fetch) -> None:
+        q, k, v = (fetch(self.name(n)) for n in ("q", "k", "v"))
+        w = torch.cat([q, self._rows_by_kv_head(k, v)], dim=0).contiguous()
+        b = None
+        if self.bias:
+            qb, kb, vb = (fetch(self.name(f"{n}.b")) for n in ("q", "k", "v"))
+            b = torch.cat([qb, self._rows_by_kv_head(kb, vb)], dim=0).contiguous()
+        self.qkv = Linear(w, b)
+        self.o = Linear(fetch(self.name("o")), fetch(self.name("o.b")) if self.bias else None)
+        if self.has_head_scale:
+            self.head_scale = fetch(self.name("temp")).contiguous()
+        if self.has_talk:
+            self.talk = fetch(self.name("talk")).contiguous()
+        if self.has_head_bias:
+            self.head_bias = fetch(self.name("pb")).contiguous()
+
+    def _attend(self, ctx: StepContext, x: torch.Tensor, view: PagedView) -> torch.Tensor:
+        qkv = self.qkv(x)  # [N, heads*dim | kv_heads*(dim + vdim)]
+        rows = view.k_cache  # [pages, page_size, kv_heads, dim + vdim]
+        if view.write:
+            window_ops.store_rows(qkv, self.heads * self.dim, self.kv_heads * self.row, rows, view.slots, ctx.status)
+        parts = window_ops.window_parts(ctx.num_tokens, self.window, self.dtype)
+        return window_ops.window_attention(qkv, rows, view.block_tables, ctx.positions, ctx.tok_seq, self.heads, self.kv_heads,
+                                           self.dim, self.vdim, self.window, self.scale, self.head_scale, self.talk,
+                                           self.head_bias, self.weights == "sigmoid", ctx.status, parts)
+
+    def mix(self, ctx: StepContext, x: torch.Tensor, view: PagedView) -> torch.Tensor:
+        return self.o.to_float32(self._attend(ctx, x, view))
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, view: PagedView, stream: ResidualStream):
+        return self.o.add_or_defer(self._attend(ctx, x, view), stream)
+
+
+register_mixer("window_attention", WindowAttention, replace=True)
