@@ -67,13 +67,15 @@ def window_mask(count, window):
     return (d >= 0) & (d < window)
 
 
-def window_scores(h, w, p, m, biased):
-    """[H, T, T] scaled scores of every query head against its key/value head, and the values [G, T, dv]."""
+def window_scores(h, w, p, m, biased, rnd=exact):
+    """[H, T, T] scaled scores of every query head against its key/value head, and the values [G, T, dv].
+    (``rnd``: a bfloat16 run stores queries, keys and values in bfloat16.)"""
     heads, groups, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     t = h.shape[0]
     q, k, v = h @ w[f"{p}.q"].T, h @ w[f"{p}.k"].T, h @ w[f"{p}.v"].T
     if biased:
         q, k, v = q + w[f"{p}.q.b"], k + w[f"{p}.k.b"], v + w[f"{p}.v.b"]
+    q, k, v = rnd(q), rnd(k), rnd(v)
     q = q.reshape(t, heads, dk).transpose(0, 1)
     k = k.reshape(t, groups, dk).transpose(0, 1)
     v = v.reshape(t, groups, dv).transpose(0, 1)
@@ -85,7 +87,7 @@ def window_scores(h, w, p, m, biased):
 
 def sigmoid_window_attention(h, w, p, m, rnd=exact):
     """The left mixer of a `parallel` layer."""
-    scores, v = window_scores(h, w, p, m, biased=True)
+    scores, v = window_scores(h, w, p, m, biased=True, rnd=rnd)
     scores = torch.einsum("hg,gts->hts", w[f"{p}.talk"], scores)
     weights = torch.sigmoid(scores + w[f"{p}.pb"][:, None, None])
     weights = weights * window_mask(h.shape[0], m["mask"]["size"])
@@ -95,7 +97,7 @@ def sigmoid_window_attention(h, w, p, m, rnd=exact):
 
 def softmax_window_attention(h, w, p, m, rnd=exact):
     """The left mixer of a `parallel_2` layer."""
-    scores, v = window_scores(h, w, p, m, biased=False)
+    scores, v = window_scores(h, w, p, m, biased=False, rnd=rnd)
     scores = scores * w[f"{p}.temp"][:, None, None]
     scores = scores.masked_fill(~window_mask(h.shape[0], m["mask"]["size"]), float("-inf"))
     o = torch.einsum("hts,hsd->thd", torch.softmax(scores, dim=-1), v).reshape(h.shape[0], -1)
@@ -169,3 +171,10 @@ def forward(config, weights, tokens, dtype=torch.float64, rnd=exact, keep_layers
         kept.append(x)
     logits = rnd(scaled_norm(x, w["final.norm"], eps)) @ w["embed"].T
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+def greedy_generate(config, weights, prompt, count, dtype=torch.float64):
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(forward(config, weights, tokens, dtype=dtype)[-1].argmax()))
+    return tokens[len(prompt):]
