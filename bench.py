@@ -367,7 +367,11 @@ def compare_designs(args) -> int:
     2,048 width (``rapitar-2k``: time mixing, latent attention, state-space layers; dense and mixture-of-experts
     feed-forwards; random weights) beside a Qwen2 decoder of the same width and layer count, through the same step
     function: a prompt of 512 and of 2,048 tokens, and single-token steps at batch 1 and 8 behind 1,024 tokens.
-    With ``--layers N`` both models have N layers.  One JSON line; device time by CUDA events, medians."""
+    With ``--design gamesun`` the design is Gamesun (``gamesun-2k``: windowed attention of 16 heads of 128 on 4
+    key/value heads beside linear attention of 16 heads, windows of 4,096 and 1,024, gated feed-forwards of 7,168)
+    beside a Qwen2 decoder of the same width, heads, layer count and feed-forward; ``--prompt-len`` sets the context
+    that the single-token steps run behind.  With ``--layers N`` both models have N layers.  One JSON line; device
+    time by CUDA events, medians."""
     import torch
 
     from clockwork_b200.cache import CacheManager
@@ -376,20 +380,24 @@ def compare_designs(args) -> int:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
-    rapitar = shape_config("rapitar-2k", args.layers)
+    shape = {"rapitar": "rapitar-2k", "gamesun": "gamesun-2k"}[args.design]
+    rapitar = shape_config(shape, args.layers)
     layers = len(rapitar["layers"])
-    qwen = dict(QWEN25_1P5B, num_hidden_layers=layers, hidden_size=2048, num_attention_heads=16, num_key_value_heads=2,
-                intermediate_size=7168, vocab_size=rapitar["vocab"], tie_word_embeddings=False)
+    qwen = dict(QWEN25_1P5B, num_hidden_layers=layers, hidden_size=2048, num_attention_heads=16,
+                num_key_value_heads=2 if args.design == "rapitar" else 4, intermediate_size=7168, vocab_size=rapitar["vocab"],
+                tie_word_embeddings=args.design == "gamesun")
     rng = random.Random(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")  # larger than L2: written between timed calls
     out = {"impl": "ours", "layers": layers, "width": 2048, "dtype": "bf16", "data": "synthetic", "l2": "flushed between timed calls"}
-    for name, raw, vocab in (("rapitar-2k", rapitar, rapitar["vocab"]), ("qwen2-2k", qwen, qwen["vocab_size"])):
+    for name, raw, vocab in ((shape, rapitar, rapitar["vocab"]), ("qwen2-2k", qwen, qwen["vocab_size"])):
+        if args.model_filter and args.model_filter not in name:
+            continue
         model = random_model(raw, seed=0, dtype="bfloat16", device="cuda:0")
-        page, ctx, batch_max = 16, 1024, 8
+        page, ctx, batch_max = 16, args.prompt_len or 1024, 8
         cache = CacheManager(model.cache_needs(), num_pages=batch_max * (ctx + 256) // page + 160, page_size=page, dtype=model.dtype,
                              device="cuda:0", num_state_slots=batch_max + 1)
         runner = ModelRunner(model, cache)
-        runner.enable_graphs(max_ctx=4096, max_batch=batch_max)
+        runner.enable_graphs(max_ctx=max(4096, ctx + 256), max_batch=batch_max)
         result = {"weight_bytes": model.weight_bytes()}
         for tokens in (512, 2048):
             times = []
@@ -448,6 +456,8 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=-1)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (reported in config)")
+    ap.add_argument("--design", choices=["rapitar", "gamesun"], default="rapitar", help="with --only designs: which design stands beside Qwen2")
+    ap.add_argument("--model-filter", default="", help="with --only designs: run only the model whose name holds this text (profiling runs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="qwen2.5-1.5b",
                     help="with --only: another size that the architecture knows by name (qwen2.5-7b, qwen2.5-32b)")

@@ -10,7 +10,9 @@
 //   cw_window_attention  one flat batch of prompt portions and single tokens; a block per (token, part of its
 //                        window); query head h reads key/value head h / (H / G); position p sees positions
 //                        max(0, p - window + 1) .. p, all of which are in the cache when the kernel runs
-//   cw_window_merge      adds up the parts of a token's window (only launched when windows are cut)
+//   (window_merge_kernel adds up the parts of a token's window; only launched when windows are cut)
+// bfloat16 calls run the tensor-core form further down when it takes the sizes; the CUDA-core kernel is the float32
+// path and the fallback.
 //
 // Scores, weights, the softmax statistics and the weighted sums are float32 in both run precisions; T names
 // the type of the product's output and of the cache.  A token's result depends on its position alone: keys
@@ -218,14 +220,14 @@ window_attention_kernel(const WindowAttentionArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions, const int* __restrict__ tok_seq,
-                    int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, T* __restrict__ out) {
+                    int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, int all_parts, T* __restrict__ out) {
     pdl_wait();
     const int n = blockIdx.x;
     if (tok_seq[n] < 0) return;  // (the attention kernel wrote the zeros)
     const int HV = H * dv, stride = HV + 2 * H;
     const int p = positions[n];
     const int keys = p + 1 - max(0, p - window + 1);
-    const int used = (keys + part_keys - 1) / part_keys;
+    const int used = all_parts ? parts : (keys + part_keys - 1) / part_keys;  // (parts that hold none of the row's keys add nothing)
     const float* base = partial + (size_t)n * parts * stride;
     for (int col = threadIdx.x; col < HV; col += blockDim.x) {
         const int h = col / dv;
@@ -247,6 +249,349 @@ window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ p
     }
 }
 
+// ---- the same on the tensor cores (bfloat16) -----------------------------------------------------------
+// A block takes 16 consecutive query rows of one request and the query heads of GC key/value heads, a warp
+// per query head (with `talk`, all heads: a weight needs every head's score of the same key).  Keys come in
+// tiles of 32 through the block table into shared memory (cp.async, two stages when they fit); scores are
+// mma.sync m16n8k16 products of bfloat16 queries and keys with float32 accumulators; scale, the heads' mix
+// (through shared memory), the numbers per head, the window's mask and the weights (online softmax, or
+// sigmoid) are float32 in registers; the weights go into the second product as two bfloat16 halves (hi + lo),
+// so that they keep 16 bits of mantissa, against the values read with ldmatrix.trans as they lie in the cache.
+// Blocks are mapped to (request, tile) by a scan of q_start, so a captured step needs nothing from the host.
+#define WM_BN 32
+
+struct WindowMmaArgs {
+    WindowAttentionArgs w;
+    const int* q_start;  // [S + 1]
+    int S, N, gc, stages, all_parts;
+};
+
+__device__ __forceinline__ void wm_ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void wm_ldmatrix_x2(unsigned (&r)[2], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void wm_ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void wm_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void wm_cp16(void* smem, const void* gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem) : "memory");
+}
+// two float32 weights as bfloat16 pairs: hi holds the rounded values, lo what the rounding left
+__device__ __forceinline__ void wm_split(float x, float y, unsigned& hi, unsigned& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - __low2float(h), y - __high2float(h));
+    hi = *reinterpret_cast<const unsigned*>(&h);
+    lo = *reinterpret_cast<const unsigned*>(&l);
+}
+
+template <int DVMAX>
+__global__ void __launch_bounds__(DVMAX > 128 ? 256 : 512)
+window_attention_mma_kernel(const WindowMmaArgs args) {
+    extern __shared__ __align__(16) unsigned char wm_smem[];
+    __shared__ int tile_seq, tile_row0, tile_rows;
+    const WindowAttentionArgs& a = args.w;
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, per = H / G, GC = args.gc;
+    const int HV = H * dv, row_width = dk + dv;
+    const int part = blockIdx.z;
+    bf16* out = (bf16*)a.out;
+    // rows of the flat batch that belong to no request (padding of a fixed-shape step) come out as zeros
+    if (blockIdx.y == 0 && part == 0) {
+        for (int i = 0; i < 16; ++i) {
+            const int n = blockIdx.x * 16 + i;
+            if (n < args.N && a.tok_seq[n] < 0)
+                for (int c = tid; c < HV; c += blockDim.x) out[(size_t)n * HV + c] = from_f<bf16>(0.f);
+        }
+    }
+    if (tid == 0) {  // which request and which 16 of its rows
+        int b = blockIdx.x, seq = -1, row0 = 0, rows = 0;
+        for (int s = 0; s < args.S; ++s) {
+            const int st = args.q_start[s], len = args.q_start[s + 1] - st;
+            if (len <= 0 || a.tok_seq[st] < 0) continue;
+            const int t = (len + 15) >> 4;
+            if (b < t) {
+                seq = s;
+                row0 = st + 16 * b;
+                rows = min(16, st + len - row0);
+                break;
+            }
+            b -= t;
+        }
+        tile_seq = seq;
+        tile_row0 = row0;
+        tile_rows = rows;
+    }
+    __syncthreads();
+    const int seq = tile_seq, row0 = tile_row0, rows = tile_rows;
+    if (seq < 0) return;
+    const int g0 = blockIdx.y * GC;
+    const int h = g0 * per + warp;  // this warp's query head
+    const int gl = warp / per;      // its key/value head among the block's
+    const int p0 = a.positions[row0];
+    const int first = max(0, p0 - a.window + 1);
+    const int lo = first + part * a.part_keys;
+    const int hi = min(p0 + rows, lo + a.part_keys);  // keys lo .. hi-1
+    // shared memory: Q [nwarps][16][dk+8], then per stage K [GC][32][dk+8] and V [GC][32][dv+8] (bfloat16), then with
+    // talk the scores of all heads [H][16][40] and the mixing matrix [H][H] (float32)
+    const int qs = dk + 8, ks_ = dk + 8, vs_ = dv + 8;
+    bf16* Qs = (bf16*)wm_smem;
+    bf16* KV = Qs + (size_t)nwarps * 16 * qs;
+    const size_t stage_elems = (size_t)GC * WM_BN * (ks_ + vs_);
+    float* Ss = (float*)(KV + (size_t)args.stages * stage_elems);
+    float* Tm = Ss + (size_t)H * 16 * 40;
+    const bool talk = a.talk != nullptr;
+    const bf16* q = (const bf16*)a.q;
+    for (int idx = tid; idx < nwarps * 16 * (dk / 8); idx += blockDim.x) {
+        const int c = idx % (dk / 8), r = (idx / (dk / 8)) % 16, w = idx / (dk / 8) / 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *(const uint4*)(q + (size_t)(row0 + r) * a.ldq + (size_t)(g0 * per + w) * dk + c * 8);
+        *(uint4*)(Qs + ((size_t)w * 16 + r) * qs + c * 8) = v;
+    }
+    if (talk)
+        for (int i = tid; i < H * H; i += blockDim.x) Tm[i] = a.talk[i];
+    const bf16* cache = (const bf16*)a.cache;
+    const int* table = a.block_tables + (size_t)seq * a.max_blocks;
+    const int chunks_per_row = row_width / 8, kchunks = dk / 8;
+    auto fetch = [&](int j0, int stage) {  // keys j0 .. j0+31 of the block's key/value heads
+        bf16* Kst = KV + (size_t)stage * stage_elems;
+        bf16* Vst = Kst + (size_t)GC * WM_BN * ks_;
+        for (int idx = tid; idx < WM_BN * GC * chunks_per_row; idx += blockDim.x) {
+            const int c = idx % chunks_per_row, rest = idx / chunks_per_row;
+            const int g = rest % GC, j = rest / GC;
+            const int pos = j0 + j;
+            bf16* dst = c < kchunks ? Kst + ((size_t)g * WM_BN + j) * ks_ + c * 8 : Vst + ((size_t)g * WM_BN + j) * vs_ + (c - kchunks) * 8;
+            int page = -1;
+            if (pos < hi) {
+                const int blk = pos / a.page_size;
+                page = blk < a.max_blocks ? table[blk] : -1;
+                if (page < 0 || page >= a.num_pages) {
+                    cw_report(a.status, CW_ST_PAGE_RANGE, row0, page);
+                    page = -1;
+                }
+            }
+            if (page >= 0) {
+                const size_t row = (size_t)page * a.page_size + pos % a.page_size;
+                wm_cp16(dst, cache + (row * G + g0 + g) * row_width + c * 8);
+            } else {
+                *(uint4*)dst = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[DVMAX / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < DVMAX / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int r_lo = lane >> 2, cpair = (lane & 3) * 2;  // this thread's rows r_lo and r_lo + 8, columns cpair, cpair + 1 of a tile of 8
+    const float head_scale = a.head_scale != nullptr ? a.head_scale[h] : 1.f;
+    const float head_bias = a.head_bias != nullptr ? a.head_bias[h] : 0.f;
+    const int nvt = dv / 8, nks = dk / 16;
+    const int ntiles = hi > lo ? (hi - lo + WM_BN - 1) / WM_BN : 0;
+    if (ntiles > 0) fetch(lo, 0);
+    for (int t = 0; t < ntiles; ++t) {
+        const int j0 = lo + t * WM_BN;
+        const int stage = args.stages == 2 ? (t & 1) : 0;
+        if (args.stages == 2 && t + 1 < ntiles) {
+            fetch(j0 + WM_BN, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // the tile has landed (and Q, at the first)
+        const bf16* Kt = KV + (size_t)stage * stage_elems + (size_t)gl * WM_BN * ks_;
+        const bf16* Vt = KV + (size_t)stage * stage_elems + (size_t)GC * WM_BN * ks_ + (size_t)gl * WM_BN * vs_;
+        float s[WM_BN / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < WM_BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int ks = 0; ks < nks; ++ks) {
+            unsigned qa[4];
+            wm_ldmatrix_x4(qa, Qs + ((size_t)warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * qs + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nt = 0; nt < WM_BN / 8; ++nt) {
+                unsigned kb[2];
+                wm_ldmatrix_x2(kb, Kt + (size_t)(nt * 8 + (lane & 7)) * ks_ + ks * 16 + ((lane >> 3) & 1) * 8);
+                wm_mma(s[nt], qa, kb[0], kb[1]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < WM_BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] *= a.scale;
+        if (talk) {  // every head's scores of this tile through shared memory, then this head's mix of them
+#pragma unroll
+            for (int nt = 0; nt < WM_BN / 8; ++nt) {
+                *(float2*)(Ss + ((size_t)h * 16 + r_lo) * 40 + nt * 8 + cpair) = make_float2(s[nt][0], s[nt][1]);
+                *(float2*)(Ss + ((size_t)h * 16 + r_lo + 8) * 40 + nt * 8 + cpair) = make_float2(s[nt][2], s[nt][3]);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int nt = 0; nt < WM_BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+            for (int g = 0; g < H; ++g) {
+                const float w = Tm[h * H + g];
+#pragma unroll
+                for (int nt = 0; nt < WM_BN / 8; ++nt) {
+                    const float2 u = *(const float2*)(Ss + ((size_t)g * 16 + r_lo) * 40 + nt * 8 + cpair);
+                    const float2 v = *(const float2*)(Ss + ((size_t)g * 16 + r_lo + 8) * 40 + nt * 8 + cpair);
+                    s[nt][0] = fmaf(w, u.x, s[nt][0]);
+                    s[nt][1] = fmaf(w, u.y, s[nt][1]);
+                    s[nt][2] = fmaf(w, v.x, s[nt][2]);
+                    s[nt][3] = fmaf(w, v.y, s[nt][3]);
+                }
+            }
+        }
+        // the window's mask and the weights
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < WM_BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = r_lo + (e >> 1) * 8, j = j0 + nt * 8 + cpair + (e & 1);
+                const int p = p0 + row;
+                const bool on = row < rows && j <= p && j > p - a.window && j < hi;
+                const float v = on ? fmaf(s[nt][e], head_scale, head_bias) : -INFINITY;
+                s[nt][e] = v;
+                tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+            }
+        if (a.sigmoid_weights) {
+#pragma unroll
+            for (int nt = 0; nt < WM_BN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = s[nt][e] == -INFINITY ? 0.f : 1.f / (1.f + __expf(-s[nt][e]));
+        } else {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                float tm = tile_max[x];
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+                tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+                const float m_new = fmaxf(m_run[x], tm);
+                const float f = m_new == -INFINITY ? 1.f : __expf(m_run[x] - m_new);
+                float sum = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < WM_BN / 8; ++nt)
+#pragma unroll
+                    for (int e = 2 * x; e < 2 * x + 2; ++e) {
+                        const float w = s[nt][e] == -INFINITY ? 0.f : __expf(s[nt][e] - m_new);
+                        s[nt][e] = w;
+                        sum += w;
+                    }
+                l_run[x] = fmaf(l_run[x], f, sum);
+                m_run[x] = m_new;
+#pragma unroll
+                for (int nt = 0; nt < DVMAX / 8; ++nt) {
+                    o[nt][2 * x] *= f;
+                    o[nt][2 * x + 1] *= f;
+                }
+            }
+        }
+        unsigned a_hi[2][4], a_lo[2][4];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            wm_split(s[2 * kk][0], s[2 * kk][1], a_hi[kk][0], a_lo[kk][0]);
+            wm_split(s[2 * kk][2], s[2 * kk][3], a_hi[kk][1], a_lo[kk][1]);
+            wm_split(s[2 * kk + 1][0], s[2 * kk + 1][1], a_hi[kk][2], a_lo[kk][2]);
+            wm_split(s[2 * kk + 1][2], s[2 * kk + 1][3], a_hi[kk][3], a_lo[kk][3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < DVMAX / 8; ++nt) {
+            if (nt < nvt) {
+                unsigned vb[4];
+                wm_ldmatrix_x4_trans(vb, Vt + (size_t)lane * vs_ + nt * 8);
+                wm_mma(o[nt], a_hi[0], vb[0], vb[1]);
+                wm_mma(o[nt], a_lo[0], vb[0], vb[1]);
+                wm_mma(o[nt], a_hi[1], vb[2], vb[3]);
+                wm_mma(o[nt], a_lo[1], vb[2], vb[3]);
+            }
+        }
+        __syncthreads();  // everyone is done with this stage (and with the shared scores)
+    }
+    // results: rows r_lo and r_lo + 8 of this warp's head
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 1);
+        l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 2);
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int row = r_lo + 8 * x;
+        if (row >= rows) continue;
+        const size_t n = (size_t)row0 + row;
+        if (a.parts > 1) {
+            float* pr = a.partial + (n * a.parts + part) * (HV + 2 * H);
+#pragma unroll
+            for (int nt = 0; nt < DVMAX / 8; ++nt)
+                if (nt < nvt) *(float2*)(pr + (size_t)h * dv + nt * 8 + cpair) = make_float2(o[nt][2 * x], o[nt][2 * x + 1]);
+            if ((lane & 3) == 0) {
+                pr[HV + h] = m_run[x];
+                pr[HV + H + h] = l_run[x];
+            }
+        } else {
+            const float inv = a.sigmoid_weights ? 1.f : (l_run[x] > 0.f ? 1.f / l_run[x] : 0.f);
+#pragma unroll
+            for (int nt = 0; nt < DVMAX / 8; ++nt)
+                if (nt < nvt)
+                    *(__nv_bfloat162*)(out + n * HV + (size_t)h * dv + nt * 8 + cpair) = __floats2bfloat162_rn(o[nt][2 * x] * inv, o[nt][2 * x + 1] * inv);
+        }
+    }
+}
+
+static int g_window_mma = 1;
+extern "C" int cw_window_attention_set_mma(int on) { g_window_mma = on ? 1 : 0; return CW_OK; }
+
+// The tensor-core form if it takes the sizes (returns 1 and launches), else 0; negative or positive: an error.
+static int window_attention_mma(const WindowAttentionArgs& base, const int* q_start, int S, int N, cudaStream_t stream, int* launched) {
+    *launched = 0;
+    const int H = base.H, G = base.G, dk = base.dk, dv = base.dv, per = H / G;
+    if (!g_window_mma || q_start == nullptr || dk % 16 || dv % 8 || dv > 256 || per > 16 || base.ldq % 8 || ((uintptr_t)base.q & 15) ||
+        ((uintptr_t)base.cache & 15))
+        return 0;
+    const int max_warps = dv > 128 ? 8 : 16;
+    int gc;
+    if (base.talk != nullptr) {
+        gc = G;
+    } else {
+        gc = per >= 4 ? 1 : min(G, 4 / per);
+        while (G % gc) --gc;
+    }
+    const int nwarps = gc * per;
+    if (nwarps > max_warps) return 0;
+    auto bytes = [&](int stages) {
+        return sizeof(bf16) * ((size_t)nwarps * 16 * (dk + 8) + (size_t)stages * gc * WM_BN * (dk + dv + 16)) +
+               (base.talk != nullptr ? sizeof(float) * ((size_t)H * 16 * 40 + (size_t)H * H) : 0);
+    };
+    int stages = 2;
+    if (bytes(2) > (200u << 10)) stages = 1;
+    const size_t smem = bytes(stages);
+    if (smem > (200u << 10)) return 0;
+    WindowMmaArgs args = {base, q_start, S, N, gc, stages, 1};
+    args.w.part_keys = ((base.window + 15 + base.parts - 1) / base.parts + WM_BN - 1) / WM_BN * WM_BN;
+    const int which = dv <= 64 ? 0 : (dv <= 128 ? 1 : 2);
+    using Kernel = void (*)(const WindowMmaArgs);
+    const Kernel kernels[3] = {window_attention_mma_kernel<64>, window_attention_mma_kernel<128>, window_attention_mma_kernel<256>};
+    static size_t allowed[3] = {48 << 10, 48 << 10, 48 << 10};
+    if (smem > allowed[which]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        allowed[which] = smem;
+    }
+    *launched = 1;
+    const dim3 grid((N + 15) / 16 + S, G / gc, base.parts);
+    return cw_launch_ordered(kernels[which], grid, dim3(nwarps * 32), smem, stream, args);
+}
+
 // How many floats of `partial` a call with these sizes needs (0: windows are not cut).
 extern "C" long long cw_window_attention_partial_words(int N, int H, int dv, int parts) {
     return parts > 1 ? (long long)N * parts * (H * dv + 2 * H) : 0;
@@ -256,13 +601,25 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
                                    int page_size, int num_pages, const int* positions, const int* tok_seq, int N, int H,
                                    int G, int dk, int dv, int window, float scale, const float* head_scale,
                                    const float* talk, const float* head_bias, int sigmoid_weights, void* out, int parts,
-                                   float* partial, int dtype, int* status, cudaStream_t stream) {
+                                   float* partial, const int* q_start, int S, int dtype, int* status, cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || window <= 0 || page_size <= 0 || max_blocks <= 0 ||
         ldq < H * dk || parts < 1)
         return CW_ERR_BAD_SIZE;
     if (parts > 1 && partial == nullptr) return CW_ERR_BAD_SIZE;
     const int HV = H * dv;
+    if (dtype == 1) {  // bfloat16: the tensor-core form when it takes the sizes
+        const WindowAttentionArgs base = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
+                                          window, scale, head_scale, talk, head_bias, sigmoid_weights, out, WM_BN, parts, 0, partial, status};
+        int launched = 0;
+        const int rc = window_attention_mma(base, q_start, S, N, stream, &launched);
+        if (rc != 0) return rc;
+        if (launched) {
+            if (parts == 1) return CW_OK;
+            return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq, H,
+                                     dv, window, parts, 0, sigmoid_weights, 1, (bf16*)out);
+        }
+    }
     int threads = 128;
     while (threads < 1024 && threads * 4 < HV) threads *= 2;      // about four output columns a thread
     while (threads * WA_MAX_COLS < HV && threads < 1024) threads *= 2;
@@ -294,9 +651,9 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     if (rc != 0 || parts == 1) return rc;
     if (dtype == 0)
         return cw_launch_ordered(window_merge_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq,
-                                 H, dv, window, parts, part_keys, sigmoid_weights, (float*)out);
+                                 H, dv, window, parts, part_keys, sigmoid_weights, 0, (float*)out);
     return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq, H,
-                             dv, window, parts, part_keys, sigmoid_weights, (bf16*)out);
+                             dv, window, parts, part_keys, sigmoid_weights, 0, (bf16*)out);
 }
 
 CW_TRACE_TU(window_attention)

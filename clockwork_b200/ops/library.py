@@ -43,7 +43,8 @@ _SIGNATURES: dict[str, list] = {
     # attention over a window of rows [key | value] (csrc/window_attention.cu); absolute positions and the sum of two normed
     # contributions (csrc/embed_norm.cu)
     "cw_store_rows": [P, I, I, I, P, P, I, LL, I, P, P],
-    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, I, P, I, P, P],
+    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, I, P, P, I, I, P, P],
+    "cw_window_attention_set_mma": [I],
     "cw_scale_add_sinusoid": [P, P, P, F, I, I, P],
     "cw_pair_rmsnorm_add": [P, P, P, P, P, F, F, I, I, P],
     # products in groups and the mixture of experts (csrc/grouped_gemm.cu)

@@ -24,6 +24,11 @@ def _partial_sums(device, heads: int, dv: int) -> torch.Tensor:
     return have
 
 
+def set_tensor_cores(on: bool) -> None:
+    """Whether bfloat16 calls may run the tensor-core form of the attention kernel (the default) or always the CUDA-core one."""
+    library().cw_window_attention_set_mma(1 if on else 0)
+
+
 def store_rows(src: torch.Tensor, col0: int, width: int, cache_rows: torch.Tensor, slots: torch.Tensor, status: torch.Tensor) -> None:
     """``cache_rows[slots[n]] = src[n, col0 : col0 + width]`` for every token n with a slot (< 0: none)."""
     if src.dim() != 2 or src.stride(1) != 1:
@@ -50,7 +55,7 @@ def reserve_window_scratch(device, heads: int, dv: int) -> None:
 
 
 def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor,
-                     tok_seq: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, window: int, scale: float,
+                     tok_seq: torch.Tensor, q_start: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, window: int, scale: float,
                      head_scale: torch.Tensor | None, talk: torch.Tensor | None, head_bias: torch.Tensor | None,
                      sigmoid_weights: bool, status: torch.Tensor, parts: int = 1) -> torch.Tensor:
     """[N, heads*dv] in ``q``'s dtype.  ``q`` [N, >= heads*dk] (queries in the leading columns, unit column stride);
@@ -61,6 +66,7 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
     if tuple(cache_rows.shape[2:]) != (kv_heads, dk + dv):
         raise ValueError(f"cache rows {tuple(cache_rows.shape)} are not [pages, page_size, {kv_heads}, {dk + dv}]")
     _need(block_tables, torch.int32, "block_tables", 2)
+    _need(q_start, torch.int32, "q_start", 1)
     for name, t, size in (("head_scale", head_scale, heads), ("talk", talk, heads * heads), ("head_bias", head_bias, heads)):
         if t is not None:
             _need(t, torch.float32, name)
@@ -77,5 +83,5 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
         _ptr(q), q.stride(0) if n > 1 else max(q.stride(0), q.shape[1]), _ptr(cache_rows), _ptr(block_tables), block_tables.shape[1],
         cache_rows.shape[1], cache_rows.shape[0], _ptr(positions), _ptr(tok_seq), n, heads, kv_heads, dk, dv, int(window), float(scale),
         _ptr(head_scale), _ptr(talk), _ptr(head_bias), 1 if sigmoid_weights else 0, _ptr(out), parts, _ptr(partial),
-        dtype_code(q.dtype), _ptr(status), _stream()), "window_attention")
+        _ptr(q_start), q_start.shape[0] - 1, dtype_code(q.dtype), _ptr(status), _stream()), "window_attention")
     return out

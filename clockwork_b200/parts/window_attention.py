@@ -107,7 +107,7 @@ class WindowAttention(Mixer):
         if view.write:
             window_ops.store_rows(qkv, self.heads * self.dim, self.kv_heads * self.row, rows, view.slots, ctx.status)
         parts = window_ops.window_parts(ctx.num_tokens, self.window, self.dtype)
-        return window_ops.window_attention(qkv, rows, view.block_tables, ctx.positions, ctx.tok_seq, self.heads, self.kv_heads,
+        return window_ops.window_attention(qkv, rows, view.block_tables, ctx.positions, ctx.tok_seq, ctx.q_start, self.heads, self.kv_heads,
                                            self.dim, self.vdim, self.window, self.scale, self.head_scale, self.talk,
                                            self.head_bias, self.weights == "sigmoid", ctx.status, parts)
 

@@ -341,6 +341,42 @@ def test_windows_cut_in_parts_when_a_step_has_few_tokens():
         assert float((cut_up - whole).abs().max()) <= 0.02 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("gated", [False, True])
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, page", [(4, 2, 32, 48, 21, 4), (16, 4, 64, 64, 70, 16), (6, 3, 64, 128, 40, 16),
+                                                                     (3, 1, 16, 40, 7, 8), (4, 4, 16, 24, 33, 8), (4, 2, 96, 192, 136, 16),
+                                                                     (2, 1, 128, 128, 300, 16)])
+def test_window_attention_on_tensor_cores(gated, heads, kv_heads, dim, vdim, window, page):
+    """The bfloat16 kernel on the tensor cores against the CUDA-core one and against the plain implementation: tiles of
+    16 rows that end in the middle of a portion, single tokens, windows that start in the middle of a tile of keys,
+    windows cut in parts (the last size)."""
+    from clockwork_b200.ops import window as window_ops
+
+    gen = torch.Generator().manual_seed(heads * 10 + window)
+    w, scale = 64, 0.25
+    t = attention_tensors(gen, w, heads, kv_heads, dim, vdim, gated)
+    for name in ("m.q", "m.k"):
+        t[name] = (t[name] * 0.6).to(torch.bfloat16).float()
+    wd = {k: v.double() for k, v in t.items()}
+    x = draw(gen, (330, w))
+    fn = plain.sigmoid_window_attention if gated else plain.softmax_window_attention
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, mask={"size": window})
+    want = fn(x.double(), wd, "m", m)
+    yard = float((fn(x.double(), wd, "m", m, rnd=plain.to_bfloat16_and_back) - want).abs().max())
+    part = part_with_weights("mixer", attention_spec(w, heads, kv_heads, dim, vdim, window, scale, gated), "m", torch.bfloat16, t)
+    for portions in ([330], [100, 1, 1, 1, 17, 16, 15, 33, 1, 145], [5] + [1] * 325):
+        outs = []
+        for on in (True, False):
+            window_ops.set_tensor_cores(on)
+            try:
+                outs.append(run_mixer(part, x, portions, page_size=page, num_pages=512))
+            finally:
+                window_ops.set_tensor_cores(True)
+        fast, slow = outs
+        assert float((fast.double() - want).abs().max()) <= 3 * yard, portions
+        assert float((slow.double() - want).abs().max()) <= 3 * yard, portions
+        assert float((fast - slow).abs().max()) <= yard, portions
+
+
 @pytest.mark.parametrize("heads, dim, vdim, rank, tau", [(3, 20, 12, 5, 8.0), (1, 64, 8, 8, 1.0), (2, 72, 40, 16, 30.0), (5, 8, 130, 3, 4.0)])
 def test_gated_linear_attention_alone(heads, dim, vdim, rank, tau):
     gen = torch.Generator().manual_seed(dim)
