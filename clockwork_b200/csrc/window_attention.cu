@@ -216,35 +216,39 @@ window_attention_kernel(const WindowAttentionArgs a) {
         }
 }
 
-// The parts of a token's window, added up in part order.
+// The parts of a token's window, added up in part order: a block per (token, head), a thread per value column.
 template <typename T>
 __global__ void __launch_bounds__(256)
 window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions, const int* __restrict__ tok_seq,
                     int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, int all_parts, T* __restrict__ out) {
+    __shared__ float factor[64];
+    __shared__ float denominator;
     pdl_wait();
-    const int n = blockIdx.x;
+    const int n = blockIdx.x, h = blockIdx.y;
     if (tok_seq[n] < 0) return;  // (the attention kernel wrote the zeros)
     const int HV = H * dv, stride = HV + 2 * H;
     const int p = positions[n];
     const int keys = p + 1 - max(0, p - window + 1);
     const int used = all_parts ? parts : (keys + part_keys - 1) / part_keys;  // (parts that hold none of the row's keys add nothing)
     const float* base = partial + (size_t)n * parts * stride;
-    for (int col = threadIdx.x; col < HV; col += blockDim.x) {
-        const int h = col / dv;
-        float sum = 0.f, l = 0.f;
-        if (sigmoid_weights) {
-            for (int s = 0; s < used; ++s) sum += base[(size_t)s * stride + col];
-            l = 1.f;
-        } else {
-            float m = -INFINITY;
+    if (threadIdx.x == 0) {
+        float m = -INFINITY, l = 0.f;
+        if (!sigmoid_weights)
             for (int s = 0; s < used; ++s) m = fmaxf(m, base[(size_t)s * stride + HV + h]);
-            for (int s = 0; s < used; ++s) {
-                const float ms = base[(size_t)s * stride + HV + h];
-                const float f = ms == -INFINITY ? 0.f : expf(ms - m);
-                sum = fmaf(f, base[(size_t)s * stride + col], sum);
-                l = fmaf(f, base[(size_t)s * stride + HV + H + h], l);
-            }
+        for (int s = 0; s < used; ++s) {
+            const float ms = base[(size_t)s * stride + HV + h];
+            const float f = sigmoid_weights ? 1.f : (ms == -INFINITY ? 0.f : expf(ms - m));
+            factor[s] = f;
+            l = fmaf(f, base[(size_t)s * stride + HV + H + h], l);
         }
+        denominator = sigmoid_weights ? 1.f : l;
+    }
+    __syncthreads();
+    const float l = denominator;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        const int col = h * dv + c;
+        float sum = 0.f;
+        for (int s = 0; s < used; ++s) sum = fmaf(factor[s], base[(size_t)s * stride + col], sum);
         out[(size_t)n * HV + col] = from_f<T>(l > 0.f ? sum / l : 0.f);
     }
 }
@@ -269,19 +273,19 @@ struct WindowMmaArgs {
 __device__ __forceinline__ void wm_ldmatrix_x4(unsigned (&r)[4], const void* p) {
     const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
 __device__ __forceinline__ void wm_ldmatrix_x2(unsigned (&r)[2], const void* p) {
     const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr) : "memory");
 }
 __device__ __forceinline__ void wm_ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
     const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
 }
 __device__ __forceinline__ void wm_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -343,8 +347,10 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     const int gl = warp / per;      // its key/value head among the block's
     const int p0 = a.positions[row0];
     const int first = max(0, p0 - a.window + 1);
-    const int lo = first + part * a.part_keys;
-    const int hi = min(p0 + rows, lo + a.part_keys);  // keys lo .. hi-1
+    // the keys that the tile's rows see, first .. p0 + rows - 1, in `parts` equal pieces of whole key tiles
+    const int part_keys = a.parts > 1 ? ((p0 + rows - first + a.parts - 1) / a.parts + WM_BN - 1) / WM_BN * WM_BN : p0 + rows - first;
+    const int lo = first + part * part_keys;
+    const int hi = min(p0 + rows, lo + part_keys);  // keys lo .. hi-1
     // shared memory: Q [nwarps][16][dk+8], then per stage K [GC][32][dk+8] and V [GC][32][dv+8] (bfloat16), then with
     // talk the scores of all heads [H][16][40] and the mixing matrix [H][H] (float32)
     const int qs = dk + 8, ks_ = dk + 8, vs_ = dv + 8;
@@ -365,29 +371,49 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
         for (int i = tid; i < H * H; i += blockDim.x) Tm[i] = a.talk[i];
     const bf16* cache = (const bf16*)a.cache;
     const int* table = a.block_tables + (size_t)seq * a.max_blocks;
+    // A thread copies the same 16-byte piece (key/value head g, piece c of the row) of every `kstep`-th key of a tile, so
+    // that what does not change from tile to tile is worked out once; pages are found by a shift when their size is a
+    // power of two.
     const int chunks_per_row = row_width / 8, kchunks = dk / 8;
-    auto fetch = [&](int j0, int stage) {  // keys j0 .. j0+31 of the block's key/value heads
+    const int pieces = GC * chunks_per_row;                     // 16-byte pieces per key
+    const bool strided = blockDim.x % pieces == 0 || pieces % blockDim.x == 0;
+    const int page_shift = (a.page_size & (a.page_size - 1)) == 0 ? 31 - __clz(a.page_size) : -1;
+    auto page_of = [&](int pos, int& offset) {
+        int blk;
+        if (page_shift >= 0) {
+            blk = pos >> page_shift;
+            offset = pos & (a.page_size - 1);
+        } else {
+            blk = pos / a.page_size;
+            offset = pos - blk * a.page_size;
+        }
+        int page = blk < a.max_blocks ? table[blk] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            cw_report(a.status, CW_ST_PAGE_RANGE, row0, page);
+            page = -1;
+        }
+        return page;
+    };
+    auto copy_piece = [&](int j, int g, int c, int pos, int stage) {
         bf16* Kst = KV + (size_t)stage * stage_elems;
         bf16* Vst = Kst + (size_t)GC * WM_BN * ks_;
-        for (int idx = tid; idx < WM_BN * GC * chunks_per_row; idx += blockDim.x) {
-            const int c = idx % chunks_per_row, rest = idx / chunks_per_row;
-            const int g = rest % GC, j = rest / GC;
-            const int pos = j0 + j;
-            bf16* dst = c < kchunks ? Kst + ((size_t)g * WM_BN + j) * ks_ + c * 8 : Vst + ((size_t)g * WM_BN + j) * vs_ + (c - kchunks) * 8;
-            int page = -1;
-            if (pos < hi) {
-                const int blk = pos / a.page_size;
-                page = blk < a.max_blocks ? table[blk] : -1;
-                if (page < 0 || page >= a.num_pages) {
-                    cw_report(a.status, CW_ST_PAGE_RANGE, row0, page);
-                    page = -1;
-                }
-            }
-            if (page >= 0) {
-                const size_t row = (size_t)page * a.page_size + pos % a.page_size;
-                wm_cp16(dst, cache + (row * G + g0 + g) * row_width + c * 8);
-            } else {
-                *(uint4*)dst = make_uint4(0, 0, 0, 0);
+        bf16* dst = c < kchunks ? Kst + ((size_t)g * WM_BN + j) * ks_ + c * 8 : Vst + ((size_t)g * WM_BN + j) * vs_ + (c - kchunks) * 8;
+        int offset = 0;
+        const int page = pos < hi ? page_of(pos, offset) : -1;
+        if (page >= 0)
+            wm_cp16(dst, cache + (((size_t)page * a.page_size + offset) * G + g0 + g) * row_width + c * 8);
+        else
+            *(uint4*)dst = make_uint4(0, 0, 0, 0);
+    };
+    const int my_piece = tid % pieces, my_g = my_piece / chunks_per_row, my_c = my_piece - my_g * chunks_per_row;
+    auto fetch = [&](int j0, int stage) {  // keys j0 .. j0+31 of the block's key/value heads
+        if (strided && blockDim.x >= pieces) {
+            for (int j = tid / pieces; j < WM_BN; j += blockDim.x / pieces) copy_piece(j, my_g, my_c, j0 + j, stage);
+        } else {
+            for (int idx = tid; idx < WM_BN * pieces; idx += blockDim.x) {
+                const int j = idx / pieces, piece = idx - j * pieces;
+                const int g = piece / chunks_per_row;
+                copy_piece(j, g, piece - g * chunks_per_row, j0 + j, stage);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -421,10 +447,11 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
             unsigned qa[4];
             wm_ldmatrix_x4(qa, Qs + ((size_t)warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * qs + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-            for (int nt = 0; nt < WM_BN / 8; ++nt) {
-                unsigned kb[2];
-                wm_ldmatrix_x2(kb, Kt + (size_t)(nt * 8 + (lane & 7)) * ks_ + ks * 16 + ((lane >> 3) & 1) * 8);
+            for (int nt = 0; nt < WM_BN / 8; nt += 2) {  // sixteen keys at a time: lanes 0-15 address the first eight, 16-31 the next
+                unsigned kb[4];
+                wm_ldmatrix_x4(kb, Kt + (size_t)(nt * 8 + (lane & 7) + (lane >> 4) * 8) * ks_ + ks * 16 + ((lane >> 3) & 1) * 8);
                 wm_mma(s[nt], qa, kb[0], kb[1]);
+                wm_mma(s[nt + 1], qa, kb[2], kb[3]);
             }
         }
 #pragma unroll
@@ -455,13 +482,19 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
         }
         // the window's mask and the weights
         float tile_max[2] = {-INFINITY, -INFINITY};
+        // (a tile that every row sees whole needs no mask: its last key is not behind the first row, its first not
+        // before the last row's window)
+        const bool whole = rows == 16 && j0 + WM_BN - 1 <= p0 && j0 > p0 + 15 - a.window && j0 + WM_BN <= hi;
 #pragma unroll
         for (int nt = 0; nt < WM_BN / 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int row = r_lo + (e >> 1) * 8, j = j0 + nt * 8 + cpair + (e & 1);
-                const int p = p0 + row;
-                const bool on = row < rows && j <= p && j > p - a.window && j < hi;
+                bool on = true;
+                if (!whole) {
+                    const int row = r_lo + (e >> 1) * 8, j = j0 + nt * 8 + cpair + (e & 1);
+                    const int p = p0 + row;
+                    on = row < rows && j <= p && j > p - a.window && j < hi;
+                }
                 const float v = on ? fmaf(s[nt][e], head_scale, head_bias) : -INFINITY;
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
@@ -505,15 +538,26 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
             wm_split(s[2 * kk + 1][0], s[2 * kk + 1][1], a_hi[kk][2], a_lo[kk][2]);
             wm_split(s[2 * kk + 1][2], s[2 * kk + 1][3], a_hi[kk][3], a_lo[kk][3]);
         }
+        // four tiles of value columns at a time, so that consecutive products go to different accumulators
 #pragma unroll
-        for (int nt = 0; nt < DVMAX / 8; ++nt) {
-            if (nt < nvt) {
-                unsigned vb[4];
-                wm_ldmatrix_x4_trans(vb, Vt + (size_t)lane * vs_ + nt * 8);
-                wm_mma(o[nt], a_hi[0], vb[0], vb[1]);
-                wm_mma(o[nt], a_lo[0], vb[0], vb[1]);
-                wm_mma(o[nt], a_hi[1], vb[2], vb[3]);
-                wm_mma(o[nt], a_lo[1], vb[2], vb[3]);
+        for (int nb = 0; nb < DVMAX / 8; nb += 4) {
+            if (nb < nvt) {
+                unsigned vb[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (nb + i < nvt) wm_ldmatrix_x4_trans(vb[i], Vt + (size_t)lane * vs_ + (nb + i) * 8);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (nb + i < nvt) wm_mma(o[nb + i], a_hi[0], vb[i][0], vb[i][1]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (nb + i < nvt) wm_mma(o[nb + i], a_lo[0], vb[i][0], vb[i][1]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (nb + i < nvt) wm_mma(o[nb + i], a_hi[1], vb[i][2], vb[i][3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (nb + i < nvt) wm_mma(o[nb + i], a_lo[1], vb[i][2], vb[i][3]);
             }
         }
         __syncthreads();  // everyone is done with this stage (and with the shared scores)
@@ -577,7 +621,6 @@ static int window_attention_mma(const WindowAttentionArgs& base, const int* q_st
     const size_t smem = bytes(stages);
     if (smem > (200u << 10)) return 0;
     WindowMmaArgs args = {base, q_start, S, N, gc, stages, 1};
-    args.w.part_keys = ((base.window + 15 + base.parts - 1) / base.parts + WM_BN - 1) / WM_BN * WM_BN;
     const int which = dv <= 64 ? 0 : (dv <= 128 ? 1 : 2);
     using Kernel = void (*)(const WindowMmaArgs);
     const Kernel kernels[3] = {window_attention_mma_kernel<64>, window_attention_mma_kernel<128>, window_attention_mma_kernel<256>};
@@ -608,6 +651,9 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
         return CW_ERR_BAD_SIZE;
     if (parts > 1 && partial == nullptr) return CW_ERR_BAD_SIZE;
     const int HV = H * dv;
+    if (parts > 64) return CW_ERR_BAD_SIZE;
+    int merge_threads = 32;
+    while (merge_threads < 256 && merge_threads < dv) merge_threads *= 2;
     if (dtype == 1) {  // bfloat16: the tensor-core form when it takes the sizes
         const WindowAttentionArgs base = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
                                           window, scale, head_scale, talk, head_bias, sigmoid_weights, out, WM_BN, parts, 0, partial, status};
@@ -616,7 +662,7 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
         if (rc != 0) return rc;
         if (launched) {
             if (parts == 1) return CW_OK;
-            return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq, H,
+            return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
                                      dv, window, parts, 0, sigmoid_weights, 1, (bf16*)out);
         }
     }
@@ -650,9 +696,9 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
                         : cw_launch_ordered(window_attention_kernel<bf16>, grid, dim3(threads), smem, stream, a);
     if (rc != 0 || parts == 1) return rc;
     if (dtype == 0)
-        return cw_launch_ordered(window_merge_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq,
+        return cw_launch_ordered(window_merge_kernel<float>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq,
                                  H, dv, window, parts, part_keys, sigmoid_weights, 0, (float*)out);
-    return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N), dim3(256), 0, stream, (const float*)partial, positions, tok_seq, H,
+    return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
                              dv, window, parts, part_keys, sigmoid_weights, 0, (bf16*)out);
 }
 

@@ -9,18 +9,23 @@ from . import _need, _ptr, _stream, dtype_code
 from .library import check, library
 
 SPLIT_MAX_PARTS = 16
-SPLIT_BELOW_TOKENS = 64  # windows are cut only in steps of fewer tokens than this
-_scratch: dict[tuple, torch.Tensor] = {}  # (device index, floats per token and part) -> the partial sums of cut windows
+SPLIT_BELOW_TOKENS = 64     # steps of fewer tokens cut windows finely: their few rows must fill the GPU
+SPLIT_LONG_KEYS = 512       # longer steps cut the keys of a row into pieces of about this many, so that rows deep in a prompt
+SPLIT_MAX_ROW_PARTS = 8192  # do not run much longer than the others; at most this many (token, part) pairs
+_scratch: dict[tuple, torch.Tensor] = {}  # (device index, floats per token and part, pairs) -> the partial sums of cut windows
 
 
-def _partial_sums(device, heads: int, dv: int) -> torch.Tensor:
-    """Room for the partial sums of the largest step whose windows are cut, made once per size and never replaced
-    (captured steps point at it)."""
+def _partial_sums(device, heads: int, dv: int, pairs: int = 0) -> torch.Tensor:
+    """Room for the partial sums of ``pairs`` (token, part) pairs, in sizes that are made once and never replaced
+    (captured steps point at them): the finest cut of a short step, or the next power of two."""
     per = heads * dv + 2 * heads
-    key = (torch.device(device).index or 0, per)
+    capacity = SPLIT_BELOW_TOKENS * SPLIT_MAX_PARTS
+    while capacity < pairs:
+        capacity *= 2
+    key = (torch.device(device).index or 0, per, capacity)
     have = _scratch.get(key)
     if have is None:
-        have = _scratch[key] = torch.empty(SPLIT_BELOW_TOKENS * SPLIT_MAX_PARTS * per, dtype=torch.float32, device=device)
+        have = _scratch[key] = torch.empty(capacity * per, dtype=torch.float32, device=device)
     return have
 
 
@@ -42,12 +47,16 @@ def store_rows(src: torch.Tensor, col0: int, width: int, cache_rows: torch.Tenso
 
 
 def window_parts(num_tokens: int, window: int, dtype: torch.dtype) -> int:
-    """In how many pieces a token's window is cut: one, unless a bfloat16 step has so few tokens that whole
-    windows per thread block would leave most of the GPU idle.  (float32 runs never cut: their results do not
-    depend on the step's size to the last bit.)"""
-    if dtype != torch.bfloat16 or num_tokens >= SPLIT_BELOW_TOKENS or window <= 256:
+    """In how many pieces the keys of a row are cut (the pieces are added up by a second kernel).  float32 runs never
+    cut: their results do not depend on the step's size to the last bit.  bfloat16: finely when a step has so few
+    tokens that whole windows per thread block would leave most of the GPU idle; coarsely in longer steps over long
+    windows, where the last rows of a prompt would otherwise run several times as long as the first."""
+    if dtype != torch.bfloat16 or window <= 256:
         return 1
-    return max(1, min(SPLIT_MAX_PARTS, window // 128, 128 // max(1, num_tokens)))
+    if num_tokens < SPLIT_BELOW_TOKENS:
+        return max(1, min(SPLIT_MAX_PARTS, window // 128, 128 // max(1, num_tokens)))
+    longest = min(window, num_tokens + window // 2)  # (keys that a row of this step may see: a guess, contexts are not known here)
+    return max(1, min(longest // SPLIT_LONG_KEYS, SPLIT_MAX_ROW_PARTS // num_tokens, SPLIT_MAX_PARTS))
 
 
 def reserve_window_scratch(device, heads: int, dv: int) -> None:
@@ -76,9 +85,9 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
     out = torch.empty((n, heads * dv), dtype=q.dtype, device=q.device)
     partial = None
     if parts > 1:
-        if n >= SPLIT_BELOW_TOKENS or parts > SPLIT_MAX_PARTS:
-            raise ValueError(f"windows are cut in at most {SPLIT_MAX_PARTS} parts and in steps of fewer than {SPLIT_BELOW_TOKENS} tokens")
-        partial = _partial_sums(q.device, heads, dv)
+        if parts > SPLIT_MAX_PARTS:
+            raise ValueError(f"windows are cut in at most {SPLIT_MAX_PARTS} parts")
+        partial = _partial_sums(q.device, heads, dv, n * parts)
     check(library().cw_window_attention(
         _ptr(q), q.stride(0) if n > 1 else max(q.stride(0), q.shape[1]), _ptr(cache_rows), _ptr(block_tables), block_tables.shape[1],
         cache_rows.shape[1], cache_rows.shape[0], _ptr(positions), _ptr(tok_seq), n, heads, kv_heads, dk, dv, int(window), float(scale),
