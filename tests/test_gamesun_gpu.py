@@ -342,8 +342,8 @@ def test_windows_cut_in_parts_when_a_step_has_few_tokens():
 
 
 @pytest.mark.parametrize("gated", [False, True])
-@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, page", [(4, 2, 32, 48, 21, 4), (16, 4, 64, 64, 70, 16), (6, 3, 64, 128, 40, 16),
-                                                                     (3, 1, 16, 40, 7, 8), (4, 4, 16, 24, 33, 8), (4, 2, 96, 192, 136, 16),
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, page", [(4, 2, 32, 48, 21, 4), (16, 4, 64, 64, 70, 16), (6, 3, 64, 96, 44, 16),
+                                                                     (3, 1, 16, 40, 7, 8), (4, 4, 16, 24, 33, 8), (4, 2, 96, 160, 100, 16),
                                                                      (2, 1, 128, 128, 300, 16)])
 def test_window_attention_on_tensor_cores(gated, heads, kv_heads, dim, vdim, window, page):
     """The bfloat16 kernel on the tensor cores against the CUDA-core one and against the plain implementation: tiles of
