@@ -1,7 +1,7 @@
 """Small Gamesun configurations of the tests and random weights for them, drawn here (tensor names and shapes are
 written out from the configuration by this file's own rules, not asked of the package).
 
-The three differ in every size, in the order of layers, and in the values that a model may happen to make equal
+The four differ in every size, in the order of layers, and in the values that a model may happen to make equal
 or 1: one key/value head for all query heads, as many key/value heads as query heads, three query heads per
 key/value head; values narrower and wider than keys; linear-attention heads whose keys and values differ in size,
 a single head; windows of 1 (a token sees itself only), smaller than a page, no multiple of a page, and longer than
@@ -53,7 +53,13 @@ CONFIG_C = _model(120, 72, 1e-5, 1.0, [
     (_gated(1, 1, 40, 8, 3, 0.15, 5, 8, 8, 12.0), _dense(88)),
     (_soft(4, 4, 16, 16, 19, 0.25, 2, 16, 16, [0.99, 0.8]), _dense(30)),
 ])
-CONFIGS = {"A": (CONFIG_A, 4, 5), "B": (CONFIG_B, 8, 8), "C": (CONFIG_C, 16, 3)}  # name -> (config, page size, decay rank)
+CONFIG_D = _model(1000, 320, 1e-6, 12.0, [  # sizes that the tensor-core attention takes, in each of its arrangements
+    (_soft(8, 2, 32, 64, 100, 32 ** -0.5, 3, 24, 40, [0.75, 0.875, 0.9375]), _dense(500)),   # four query heads per key/value head
+    (_gated(12, 3, 48, 80, 60, 48 ** -0.5, 2, 32, 64, 4.0), _dense(260)),                    # twelve heads mixed: twelve warps a block
+    (_gated(20, 4, 16, 24, 64, 0.25, 5, 16, 16, 16.0), None),                                # twenty heads mixed: the CUDA-core kernel
+    (_soft(4, 4, 80, 200, 30, 80 ** -0.5, 4, 64, 32, [0.5, 0.9, 0.99, 0.999]), _dense(384)),  # one query head per key/value head, wide values
+])
+CONFIGS = {"A": (CONFIG_A, 4, 5), "B": (CONFIG_B, 8, 8), "C": (CONFIG_C, 16, 3), "D": (CONFIG_D, 16, 6)}  # name -> (config, page size, decay rank)
 
 
 def tensor_shapes(config: dict, decay_rank: int) -> dict[str, tuple]:

@@ -178,3 +178,28 @@ def greedy_generate(config, weights, prompt, count, dtype=torch.float64):
     for _ in range(count):
         tokens.append(int(forward(config, weights, tokens, dtype=dtype)[-1].argmax()))
     return tokens[len(prompt):]
+
+
+def first_position_margin(config, weights, token, dtype=torch.float64):
+    """At position 0 a head of the linear attention with a norm per head puts out sign(q.k) n(v): the smallest
+    |cos(q, k)| over those heads says how far the first token is from a sign that rounding could flip."""
+    w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
+    eps = config["norm"]["eps"]
+    x = embed(torch.as_tensor([token], dtype=torch.long), w, config["embedding"]["scale"], dtype)
+    margin = 1.0
+    for i, layer in enumerate(config["layers"]):
+        h = scaled_norm(x, w[f"l{i}.norm1"], eps)
+        if layer["type"] == "parallel":
+            m = layer["mixer"]["right"]
+            q = (h @ w[f"l{i}.mix.right.q"].T).reshape(m["heads"], m["dim"])
+            k = (h @ w[f"l{i}.mix.right.k"].T).reshape(m["heads"], m["dim"])
+            margin = min(margin, float(((q * k).sum(-1) / (q.norm(dim=-1) * k.norm(dim=-1))).abs().min()))
+        x = x + side_by_side(h, w, f"l{i}.mix", layer["type"], layer["mixer"], eps)
+        if layer.get("mlp") is not None:
+            x = x + gated_ff(scaled_norm(x, w[f"l{i}.norm2"], eps), w, f"l{i}.mlp")
+    return margin
+
+
+def steady_first_token(config, weights, candidates=range(48)):
+    """The candidate whose answer at position 0 is farthest from such a flip."""
+    return max(candidates, key=lambda token: first_position_margin(config, weights, token))
