@@ -7,9 +7,17 @@ Parameters: ``hidden_size, eps, factor`` (0.5: half the sum), ``left`` and ``rig
 registered mixer that has ``mix``).  Tensors: the mixers' own under ``<prefix>.left`` and ``<prefix>.right``, and the
 two weights ``left.out`` and ``right.out`` [hidden].  What the two keep per request is asked for as a tuple (pages
 of the one, a state slot of the other); the norms and the sum into the residual are one float32 kernel.
+
+The two mixers share nothing but their input, so the left one's kernels are launched on a second stream of the device
+and meet the right one's at the kernel that adds both up (``SideBySide.concurrent = False``: one after the other on
+the step's stream; the results are the same bits).  In a captured step the two chains become parallel branches of the
+graph.  Every tensor the left mixer makes is made and last used inside that fork and join, so the allocator's
+per-stream pools never hand memory on while the other stream still reads it.
 """
 
 from __future__ import annotations
+
+import torch
 
 from .. import ops
 from ..weights.decl import TensorDecl
@@ -17,7 +25,20 @@ from .base import Mixer, PagedKVNeed, ResidualStream, SlotStateNeed, StepContext
 from .registry import build_part, register_mixer
 
 
+_side_streams: dict[int, "torch.cuda.Stream"] = {}  # one second stream per device, shared by every layer
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    stream = _side_streams.get(index)
+    if stream is None:
+        stream = _side_streams[index] = torch.cuda.Stream(device=index)
+    return stream
+
+
 class SideBySide(Mixer):
+    concurrent = True  # the left mixer on a second stream beside the right one
+
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
         p = spec.params
@@ -36,6 +57,7 @@ class SideBySide(Mixer):
             if sum(isinstance(n, kind) for n in needs) > 1:
                 raise ValueError(f"both mixers of {prefix!r} keep {kind.__name__}: one layer has one of each at most")
         self._needs = needs
+        self._forked = self._joined = None  # events of the fork and the join (made at first use)
 
     def cache_need(self):
         kept = tuple(n for n in self._needs if n is not None)
@@ -71,8 +93,20 @@ class SideBySide(Mixer):
 
     def forward(self, ctx: StepContext, x, view, stream: ResidualStream):
         left_view, right_view = self._views(view)
-        a = self.left.mix(ctx, x, left_view)
-        b = self.right.mix(ctx, x, right_view)
+        if self.concurrent and x.is_cuda:
+            if self._forked is None:
+                self._forked, self._joined = torch.cuda.Event(), torch.cuda.Event()
+            main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
+            self._forked.record(main)
+            side.wait_event(self._forked)  # x is ready (and everything the step's stream did before)
+            with torch.cuda.stream(side):
+                a = self.left.mix(ctx, x, left_view)
+                self._joined.record(side)
+            b = self.right.mix(ctx, x, right_view)
+            main.wait_event(self._joined)
+        else:
+            a = self.left.mix(ctx, x, left_view)
+            b = self.right.mix(ctx, x, right_view)
         ops.pair_rmsnorm_add(stream.residual_after_flush(), a, b, self.left_weight, self.right_weight, self.eps, self.factor)
         return None
 

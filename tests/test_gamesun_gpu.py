@@ -437,6 +437,27 @@ def test_decay_linear_attention_alone(heads, dim, vdim, decay):
         assert_close(got, want, portions)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_two_mixers_on_two_streams_change_nothing(dtype, dirs):
+    """The left mixer's kernels run on a second stream beside the right one's: the same bits as one after the other,
+    in prompts, portions and captured single-token steps."""
+    from clockwork_b200.parts.side_by_side import SideBySide
+
+    name = "D"
+    tokens = tokens_for(CONFIGS[name][0], 120, salt=15)
+    results = []
+    for concurrent in (True, False):
+        SideBySide.concurrent = concurrent
+        try:
+            run = Replay(dirs[name], name, dtype, 256)
+            for portion in cut(tokens, [70, 3, 17, 1, 1, 1, 1, 1, 25]):
+                run.step({"a": portion})
+            results.append(run.of("a"))
+        finally:
+            SideBySide.concurrent = True
+    assert torch.equal(results[0], results[1])
+
+
 @pytest.mark.parametrize("kind", ["parallel", "parallel_2"])
 def test_two_mixers_side_by_side_alone(kind):
     """Pages for the one and a state slot for the other in the same layer; each output normed over the width."""
